@@ -419,6 +419,107 @@ int b200_lm_head_topk_sample(b200_decoder_t *dec, const void *hidden, const void
                              int *output_id, int batch, int k, int step, int end_id,
                              b200_stream_t stream);
 
+/* ============================= layer-list decoder: mixed token mixers + mixture-of-experts feed-forward =============================
+ * (absent from the reference, whose only model is the Llama-2 decoder of src/models/llama/llama.cpp.)  A decoder whose layers are
+ * described one by one: every layer has a token mixer of some kind (b200_mixer_kind_t) and, optionally, a feed-forward of some kind
+ * (b200_mlp_kind_t); its sizes and constants are fields of the layer, so one engine serves any order and any sizes.  The residual stream
+ * is fp32 and the norm sits on the sublayer OUTPUT:  x += rmsnorm(mixer(x)) * g1;  x += rmsnorm(ff(x)) * g2.
+ * One forward call runs a RAGGED, MIXED batch: every sequence brings a portion of consecutive tokens (a whole prompt, a piece of one,
+ * or a single decoded token) that continues from what earlier calls left in the paged key/value pool (attention layers) and in the
+ * sequence's state slot (recurrent layers).  Prefill and decode are the same call. */
+typedef enum {
+    B200_MIXER_ATTN_CHUNKED = 1, /* softmax attention, no rotation, block-diagonal causal mask, optional sink, sigmoid output gate      */
+    B200_MIXER_GLA = 2           /* gated linear attention: per-key-channel decay, fp32 matrix state per head                         */
+} b200_mixer_kind_t;
+typedef enum { B200_MLP_NONE = 0, B200_MLP_MOE = 1 } b200_mlp_kind_t;
+typedef enum { B200_ACT_RELU2 = 0, B200_ACT_SILU = 1, B200_ACT_GELU_TANH = 2 } b200_act_t;
+
+typedef struct {
+    int width, vocab, num_layers;
+    int dtype;          /* weights, projections and caches: B200_F32 / B200_F16 / B200_BF16; the residual, norms, softmax, routers and
+                           recurrent state are fp32 whatever this says                                                               */
+    float norm_eps;
+    int max_tokens;     /* tokens of one forward call (sizes the scratch)                                                             */
+    int max_seqs;       /* sequences of one forward call                                                                              */
+    int max_pages_per_seq;
+} b200_hybrid_config_t;
+
+typedef struct {
+    int mixer;          /* b200_mixer_kind_t                                                                                          */
+    int heads, kv_heads, dim, vdim;
+    float scale;        /* ATTN: score scale                                                                                          */
+    int chunk;          /* ATTN: position i sees j <= i with floor(i/chunk) == floor(j/chunk); 0 = plain causal                       */
+    float tau;          /* GLA: decay = sigmoid(z)^(1/tau)                                                                            */
+    int decay_rank;     /* GLA: inner size of the low-rank decay projection                                                           */
+    int mlp;            /* b200_mlp_kind_t                                                                                            */
+    int experts, top, expert_ff, shared_ff; /* MOE; shared_ff == 0: no shared expert                                                  */
+    int act;            /* b200_act_t of the experts                                                                                  */
+    /* ---- weights: matrices [out, in] row-major of the engine dtype, vectors fp32 */
+    const void *w_in;   /* ATTN: rows q (heads*dim), k (kv_heads*dim), gate (heads*dim);  GLA: rows q, k (heads*dim each), v, gate
+                           (heads*vdim each), decay-in (decay_rank).  K = width                                                       */
+    const void *w_out;  /* [width, heads*vdim]                                                                                        */
+    const float *q_norm, *k_norm; /* ATTN: [heads*dim], [kv_heads*dim]: RMS norm over the WHOLE projection                            */
+    const float *sink;  /* ATTN: [heads] or NULL                                                                                      */
+    const void *w_decay; const float *decay_bias; /* GLA: [heads*dim, decay_rank], [heads*dim]                                        */
+    const float *out_norm;        /* GLA: [vdim], shared by the heads                                                                 */
+    const float *norm1, *norm2;   /* [width]                                                                                          */
+    const void *w_router;         /* MOE: [experts + 1, width]: router rows, then the shared expert's gate row (zeros if none)        */
+    const void *w_up, *w_down;    /* MOE: [experts, expert_ff, width], [experts, width, expert_ff]                                    */
+    const void *w_shared_up, *w_shared_down; /* [shared_ff, width], [width, shared_ff]                                                */
+} b200_hybrid_layer_t;
+
+typedef struct {
+    int n_tokens, n_seqs, n_want;
+    const int *token_ids;   /* HOST [n_tokens]: the sequences' portions packed back to back                                           */
+    const int *seq_start;   /* HOST [n_seqs + 1]: packed row of each portion's first token                                            */
+    const int *seq_pos0;    /* HOST [n_seqs]: position (from 0) of that token in its sequence                                         */
+    const int *seq_slot;    /* HOST [n_seqs]: recurrent-state slot                                                                    */
+    const int *block_table; /* HOST [n_seqs, max_pages_per_seq]: pages of B200_KV_PAGE_SIZE positions, -1 where none                  */
+    const int *want_rows;   /* HOST [n_want]: packed rows whose logits are produced                                                   */
+} b200_hybrid_batch_t;
+
+typedef struct b200_hybrid b200_hybrid_t;
+b200_hybrid_t *b200_hybrid_create(const b200_hybrid_config_t *cfg);
+void b200_hybrid_destroy(b200_hybrid_t *m);
+int b200_hybrid_set_layer(b200_hybrid_t *m, int layer, const b200_hybrid_layer_t *w);
+/* embedding [vocab, width], lm_head [vocab, width] (engine dtype), final_norm fp32 [width] */
+int b200_hybrid_set_io(b200_hybrid_t *m, const void *embedding, const float *final_norm, const void *lm_head);
+size_t b200_hybrid_scratch_bytes(const b200_hybrid_t *m);
+int b200_hybrid_set_scratch(b200_hybrid_t *m, void *ptr, size_t bytes);
+/* Key/value pool: per attention layer K [num_pages, kv_heads, B200_KV_PAGE_SIZE, dim] then V, of the engine dtype (layers may differ in
+ * size; each starts 256-byte aligned).  State pool: per recurrent layer fp32 [num_slots, heads, dim, vdim].  Caller-owned. */
+size_t b200_hybrid_kv_pool_bytes(const b200_hybrid_t *m, int num_pages);
+size_t b200_hybrid_state_pool_bytes(const b200_hybrid_t *m, int num_slots);
+int b200_hybrid_set_pools(b200_hybrid_t *m, void *kv_pool, int num_pages, void *state_pool, int num_slots);
+/* logits: DEVICE fp32 [n_want, vocab] (may be NULL when n_want == 0).  layer_trace (optional): DEVICE fp32 [num_layers, n_tokens, width],
+ * the residual stream after every layer.  Stream-ordered, allocation-free; the host arrays may be reused when the call returns. */
+int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *batch, float *logits, float *layer_trace, b200_stream_t stream);
+
+/* ---- the mechanisms, one launcher each (the engine calls exactly these) */
+/* Whole-projection RMS norm of q and k + append to the paged pool.  proj [tokens, ld]: q at column 0, k at column heads*dim.
+ * q_out [tokens, heads*dim] = q * rsqrt(mean(q^2) + eps) * q_norm;  k_pool row <- the same for k;  v_pool row <- k as projected.
+ * q_norm / k_norm NULL: no norm.  tok_seq / tok_pos: DEVICE [tokens]. */
+int b200_attn_qk_norm_cache_paged(const void *proj, int ld, void *q_out, void *k_pool, void *v_pool, const float *q_norm,
+                                  const float *k_norm, float eps, const int *tok_seq, const int *tok_pos, const int *block_table,
+                                  int max_pages_per_seq, int tokens, int heads, int kv_heads, int dim, int dtype, b200_stream_t stream);
+/* out[t, h*dim + c] = gate * sum_j p_j v[j, g(h), c],  p = softmax over {scale * q.k_j : j in the chunk of pos(t), j <= pos(t)} with
+ * exp(sink[h]) added to the denominator (sink NULL: none);  gate = sigmoid(gate_in[t*gate_ld + h*dim + c]) (gate_in NULL: 1). */
+int b200_chunked_attention_paged(const void *q, const void *k_pool, const void *v_pool, const float *sink, const void *gate_in,
+                                 int gate_ld, void *out, const int *tok_seq, const int *tok_pos, const int *block_table,
+                                 int max_pages_per_seq, int tokens, int heads, int kv_heads, int dim, float scale, int chunk,
+                                 int dtype, b200_stream_t stream);
+/* Gated-linear-attention recurrence over every sequence's portion: S <- diag(a_t) S + k_t v_t^T;  o_t = S^T (q_t * dim^-1/2).
+ * proj [tokens, ld]: q at column 0, k at heads*dim, v at 2*heads*dim.  decay: fp32 [tokens, heads*dim] (a_t).
+ * state: fp32 [num_slots, heads, dim, vdim], read unless the portion starts at position 0, written back at the end.
+ * o: fp32 [tokens, heads*vdim].  seq_start / seq_pos0 / seq_slot: DEVICE. */
+int b200_gla_recurrent(const void *proj, int ld, const float *decay, float *state, float *o, const int *seq_start, const int *seq_pos0,
+                       const int *seq_slot, int n_seqs, int heads, int dim, int vdim, int dtype, b200_stream_t stream);
+/* Router of a sigmoid-scored mixture of experts.  logits fp32 [tokens, ld] (experts router columns, then the shared gate at column
+ * `experts`).  sel_expert / sel_weight [tokens, top]: the `top` largest scores (ties: lower index), weights = the scores themselves.
+ * shared_gate [tokens] = sigmoid(logits[:, experts]). */
+int b200_moe_route_sigmoid(const float *logits, int ld, int *sel_expert, float *sel_weight, float *shared_gate, int tokens, int experts,
+                           int top, b200_stream_t stream);
+
 /* ========================================== generation loop ========================================= */
 
 /* The loop LlamaModel<T>::response / generateFirstToken / generateNextToken / LMHeadAndTopKSample intend
@@ -492,7 +593,15 @@ enum {
     B200_PLAN_DECODE_TOKENS = 5,       /* int[n_decode]: the token each running sequence feeds                               */
     B200_PLAN_DECODE_STEPS = 6,        /* int[n_decode]: its 1-based position count including that token                     */
     B200_PLAN_DECODE_REQUESTS = 7,
-    B200_PLAN_DECODE_BLOCK_TABLE = 8
+    B200_PLAN_DECODE_BLOCK_TABLE = 8,
+    /* the mixed plan (b200_batcher_plan_mixed): n = n_prefill + n_decode rows, one per sequence that brings a portion */
+    B200_PLAN_MIXED_IDS = 16,          /* int[prefill_tokens]: the portions packed back to back                              */
+    B200_PLAN_MIXED_STARTS = 17,       /* int[n + 1]: packed row of every portion's first token                              */
+    B200_PLAN_MIXED_POS0 = 18,         /* int[n]: position of that token in its sequence                                     */
+    B200_PLAN_MIXED_SLOTS = 19,        /* int[n]: recurrent-state slot                                                       */
+    B200_PLAN_MIXED_REQUESTS = 20,
+    B200_PLAN_MIXED_BLOCK_TABLE = 21,  /* int[n, max_pages_per_seq]                                                          */
+    B200_PLAN_MIXED_SAMPLE_ROWS = 22   /* int[n]: packed row to sample from if the portion ends the sequence's tokens, else -1 */
 };
 
 /* ---- scheduler: host only, no CUDA call (tests/test_batcher.py drives it on a CPU-only box) */
@@ -525,6 +634,36 @@ int b200_batcher_preemptions(const b200_batcher_t *b, int request);
 size_t b200_batcher_workspace_bytes(const b200_batcher_t *b, const b200_decoder_t *dec, const b200_generate_params_t *p);
 int b200_batcher_step(b200_batcher_t *b, b200_decoder_t *dec, const b200_generate_params_t *p, void *k_pool, void *v_pool,
                       void *workspace, size_t workspace_bytes, int *n_finished, b200_stream_t stream);
+
+/* ---- recurrent-state slots, prompts read in portions, sequences driven by the caller (models served by the layer-list decoder) */
+/* Gives the scheduler `num_slots` state slots: a sequence holds one from admission until its pages return. */
+int b200_batcher_set_state_slots(b200_batcher_t *b, int num_slots);
+int b200_batcher_free_slots(const b200_batcher_t *b);
+/* Most tokens one sequence brings to one mixed iteration (0: as many as the token budget allows). */
+int b200_batcher_set_chunk(b200_batcher_t *b, int max_tokens_per_sequence);
+/* The mixed plan: ONE ragged batch per iteration -- every running sequence's next portion (the single token of a decoding one, or the
+ * next piece of a prompt still being read) and the first portions of newly admitted ones, within the budget max_prefill_tokens.  Pages
+ * are taken portion by portion; a sequence is sampled in the iteration whose portion reaches its last token.  In the returned plan
+ * n_prefill + n_decode is the number of rows, prefill_tokens the packed token count, decode_max_step the longest position reached. */
+int b200_batcher_plan_mixed(b200_batcher_t *b, b200_batch_plan_t *plan);
+int b200_batcher_commit_mixed(b200_batcher_t *b, const int *sampled, int end_id);
+int b200_batcher_abort_mixed(b200_batcher_t *b);
+/* A sequence whose tokens the CALLER brings portion by portion (a replayed trace, a prompt that is still arriving).  It shares pages and
+ * slots with the planner's sequences but is never planned, sampled or preempted.  attach -> request id (or a negative error: no slot);
+ * extend takes the pages of n more positions and returns the first one's position; release gives pages and slot back. */
+int b200_batcher_attach(b200_batcher_t *b);
+int b200_batcher_extend(b200_batcher_t *b, int request, const int *tokens, int n, int *pos0);
+int b200_batcher_release(b200_batcher_t *b, int request);
+/* row: int[max_pages_per_seq] (-1 where no page is held); slot: the state slot (-1: none).  Either may be NULL. */
+int b200_batcher_seq_pages(const b200_batcher_t *b, int request, int *row, int *slot);
+
+/* One mixed iteration on the layer-list decoder: plan_mixed -> b200_hybrid_forward over the whole ragged batch (portions of prompts
+ * beside single decoded tokens) -> top-k / sampling on the rows that end a sequence's tokens -> commit.  The model's pools were given to
+ * it by b200_hybrid_set_pools (num_pages / num_slots as this scheduler's).  workspace: b200_batcher_hybrid_workspace_bytes, 256-byte
+ * aligned device memory.  Synchronises the stream. */
+size_t b200_batcher_hybrid_workspace_bytes(const b200_batcher_t *b, int vocab, int top_k);
+int b200_batcher_step_hybrid(b200_batcher_t *b, b200_hybrid_t *model, int vocab, int top_k, int end_id, void *workspace,
+                             size_t workspace_bytes, int *n_finished, b200_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -58,6 +58,35 @@ class BatchPlan(C.Structure):
                 ("decode_max_step", C.c_int), ("n_preempted", C.c_int), ("free_pages", C.c_int), ("n_waiting", C.c_int)]
 
 
+class HybridConfig(C.Structure):
+    """b200_hybrid_config_t (include/b200llm.h)."""
+    _fields_ = [("width", C.c_int), ("vocab", C.c_int), ("num_layers", C.c_int), ("dtype", C.c_int), ("norm_eps", C.c_float),
+                ("max_tokens", C.c_int), ("max_seqs", C.c_int), ("max_pages_per_seq", C.c_int)]
+
+
+class HybridLayer(C.Structure):
+    """b200_hybrid_layer_t (include/b200llm.h)."""
+    _fields_ = [("mixer", C.c_int), ("heads", C.c_int), ("kv_heads", C.c_int), ("dim", C.c_int), ("vdim", C.c_int), ("scale", C.c_float),
+                ("chunk", C.c_int), ("tau", C.c_float), ("decay_rank", C.c_int), ("mlp", C.c_int), ("experts", C.c_int), ("top", C.c_int),
+                ("expert_ff", C.c_int), ("shared_ff", C.c_int), ("act", C.c_int),
+                ("w_in", C.c_void_p), ("w_out", C.c_void_p), ("q_norm", C.c_void_p), ("k_norm", C.c_void_p), ("sink", C.c_void_p),
+                ("w_decay", C.c_void_p), ("decay_bias", C.c_void_p), ("out_norm", C.c_void_p), ("norm1", C.c_void_p), ("norm2", C.c_void_p),
+                ("w_router", C.c_void_p), ("w_up", C.c_void_p), ("w_down", C.c_void_p), ("w_shared_up", C.c_void_p),
+                ("w_shared_down", C.c_void_p)]
+
+
+class HybridBatch(C.Structure):
+    """b200_hybrid_batch_t (include/b200llm.h): host arrays."""
+    _fields_ = [("n_tokens", C.c_int), ("n_seqs", C.c_int), ("n_want", C.c_int), ("token_ids", C.c_void_p), ("seq_start", C.c_void_p),
+                ("seq_pos0", C.c_void_p), ("seq_slot", C.c_void_p), ("block_table", C.c_void_p), ("want_rows", C.c_void_p)]
+
+
+MIXER_ATTN_CHUNKED, MIXER_GLA = 1, 2
+MLP_NONE, MLP_MOE = 0, 1
+ACT_RELU2, ACT_SILU, ACT_GELU_TANH = 0, 1, 2
+(PLAN_MIXED_IDS, PLAN_MIXED_STARTS, PLAN_MIXED_POS0, PLAN_MIXED_SLOTS, PLAN_MIXED_REQUESTS, PLAN_MIXED_BLOCK_TABLE,
+ PLAN_MIXED_SAMPLE_ROWS) = range(16, 23)
+
 KV_PAGE_SIZE = 64
 REQ_WAITING, REQ_RUNNING, REQ_FINISHED, REQ_REJECTED = 0, 1, 2, 3
 (PLAN_PREFILL_IDS, PLAN_PREFILL_LENS, PLAN_PREFILL_REQUESTS, PLAN_PREFILL_BLOCK_TABLE, PLAN_PREFILL_LAST_ROWS, PLAN_DECODE_TOKENS,
@@ -140,11 +169,39 @@ SIGNATURES = {
     "b200_batcher_preemptions": [_P, _I],
     "b200_batcher_workspace_bytes": [_P, _P, C.POINTER(GenerateParams)],
     "b200_batcher_step": [_P, _P, C.POINTER(GenerateParams), _P, _P, _P, _SZ, C.POINTER(C.c_int), _P],
+    "b200_hybrid_create": [C.POINTER(HybridConfig)],
+    "b200_hybrid_destroy": [_P],
+    "b200_hybrid_set_layer": [_P, _I, C.POINTER(HybridLayer)],
+    "b200_hybrid_set_io": [_P, _P, _P, _P],
+    "b200_hybrid_scratch_bytes": [_P],
+    "b200_hybrid_set_scratch": [_P, _P, _SZ],
+    "b200_hybrid_kv_pool_bytes": [_P, _I],
+    "b200_hybrid_state_pool_bytes": [_P, _I],
+    "b200_hybrid_set_pools": [_P, _P, _I, _P, _I],
+    "b200_hybrid_forward": [_P, C.POINTER(HybridBatch), _P, _P, _P],
+    "b200_attn_qk_norm_cache_paged": [_P, _I, _P, _P, _P, _P, _P, _F, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "b200_chunked_attention_paged": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
+    "b200_gla_recurrent": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "b200_moe_route_sigmoid": [_P, _I, _P, _P, _P, _I, _I, _I, _P],
+    "b200_batcher_set_state_slots": [_P, _I],
+    "b200_batcher_free_slots": [_P],
+    "b200_batcher_set_chunk": [_P, _I],
+    "b200_batcher_plan_mixed": [_P, C.POINTER(BatchPlan)],
+    "b200_batcher_commit_mixed": [_P, _P, _I],
+    "b200_batcher_abort_mixed": [_P],
+    "b200_batcher_attach": [_P],
+    "b200_batcher_extend": [_P, _I, _P, _I, C.POINTER(C.c_int)],
+    "b200_batcher_release": [_P, _I],
+    "b200_batcher_seq_pages": [_P, _I, _P, C.POINTER(C.c_int)],
+    "b200_batcher_hybrid_workspace_bytes": [_P, _I, _I],
+    "b200_batcher_step_hybrid": [_P, _P, _I, _I, _I, _P, _SZ, C.POINTER(C.c_int), _P],
 }
 _RESTYPES = {"b200_last_error_string": C.c_char_p, "b200_workspace_default_bytes": _SZ, "b200_decoder_create": _P,
              "b200_decoder_destroy": None, "b200_decoder_scratch_bytes": _SZ, "b200_decoder_prefill_scratch_bytes": _SZ,
              "b200_decoder_tp_buffer_bytes": _SZ, "b200_generate_workspace_bytes": _SZ, "b200_batcher_create": _P,
-             "b200_batcher_destroy": None, "b200_batcher_plan_array": C.POINTER(C.c_int), "b200_batcher_workspace_bytes": _SZ}
+             "b200_batcher_destroy": None, "b200_batcher_plan_array": C.POINTER(C.c_int), "b200_batcher_workspace_bytes": _SZ,
+             "b200_hybrid_create": _P, "b200_hybrid_destroy": None, "b200_hybrid_scratch_bytes": _SZ, "b200_hybrid_kv_pool_bytes": _SZ,
+             "b200_hybrid_state_pool_bytes": _SZ, "b200_batcher_hybrid_workspace_bytes": _SZ}
 
 _lib = None
 
@@ -738,4 +795,80 @@ class Batcher:
         fin = C.c_int(0)
         check(lib().b200_batcher_step(self.handle, dec.handle, C.byref(gp), ptr(k_pool), ptr(v_pool), C.c_void_p(base), self._ws_bytes,
                                       C.byref(fin), stream()))
+        return fin.value
+
+    # ---- state slots, portions, caller-driven sequences (models served by the layer-list decoder)
+    def set_state_slots(self, num_slots):
+        check(lib().b200_batcher_set_state_slots(self.handle, int(num_slots)))
+
+    def free_slots(self):
+        return lib().b200_batcher_free_slots(self.handle)
+
+    def set_chunk(self, max_tokens_per_sequence):
+        check(lib().b200_batcher_set_chunk(self.handle, int(max_tokens_per_sequence)))
+
+    def attach(self):
+        rid = lib().b200_batcher_attach(self.handle)
+        if rid < 0:
+            raise B200Error(f"b200 status {rid}: {lib().b200_last_error_string().decode()}")
+        return rid
+
+    def extend(self, request, tokens):
+        import numpy as np
+
+        ids = np.ascontiguousarray(np.asarray(tokens, dtype=np.int32))
+        pos0 = C.c_int(0)
+        check(lib().b200_batcher_extend(self.handle, int(request), ids.ctypes.data_as(C.c_void_p), int(ids.size), C.byref(pos0)))
+        return pos0.value
+
+    def release(self, request):
+        check(lib().b200_batcher_release(self.handle, int(request)))
+
+    def seq_pages(self, request):
+        import numpy as np
+
+        row = np.zeros(self.cfg.max_pages_per_seq, np.int32)
+        slot = C.c_int(-1)
+        check(lib().b200_batcher_seq_pages(self.handle, int(request), row.ctypes.data_as(C.c_void_p), C.byref(slot)))
+        return row, slot.value
+
+    def plan_mixed(self):
+        import numpy as np
+
+        p = BatchPlan()
+        check(lib().b200_batcher_plan_mixed(self.handle, C.byref(p)))
+        n, mp = p.n_prefill + p.n_decode, self.cfg.max_pages_per_seq
+
+        def arr(which, k):
+            if k == 0:
+                return np.zeros(0, np.int32)
+            return np.ctypeslib.as_array(lib().b200_batcher_plan_array(self.handle, which), shape=(k,)).copy()
+
+        views = dict(ids=arr(PLAN_MIXED_IDS, p.prefill_tokens), starts=arr(PLAN_MIXED_STARTS, n + 1), pos0=arr(PLAN_MIXED_POS0, n),
+                     slots=arr(PLAN_MIXED_SLOTS, n), requests=arr(PLAN_MIXED_REQUESTS, n),
+                     block_table=arr(PLAN_MIXED_BLOCK_TABLE, n * mp).reshape(n, mp), sample_rows=arr(PLAN_MIXED_SAMPLE_ROWS, n))
+        return p, views
+
+    def commit_mixed(self, sampled, end_id):
+        import numpy as np
+
+        a = np.ascontiguousarray(np.asarray(sampled, dtype=np.int32))
+        n = lib().b200_batcher_commit_mixed(self.handle, a.ctypes.data_as(C.c_void_p), int(end_id))
+        if n < 0:
+            raise B200Error(f"b200 status {n}: {lib().b200_last_error_string().decode()}")
+        return n
+
+    def step_hybrid(self, model, top_k=1, end_id=-1):
+        """One mixed iteration on a layer-list decoder (b200_batcher_step_hybrid); returns the number of requests it finished."""
+        torch = _torch()
+        ensure_workspace()
+        vocab = model.cfg.vocab
+        if getattr(self, "_hws", None) is None:
+            nbytes = lib().b200_batcher_hybrid_workspace_bytes(self.handle, vocab, int(top_k))
+            self._hws = torch.empty(nbytes + 256, dtype=torch.uint8, device=model.device)
+            self._hws_bytes = nbytes
+        base = (self._hws.data_ptr() + 255) // 256 * 256
+        fin = C.c_int(0)
+        check(lib().b200_batcher_step_hybrid(self.handle, model.handle, vocab, int(top_k), int(end_id), C.c_void_p(base), self._hws_bytes,
+                                             C.byref(fin), stream()))
         return fin.value

@@ -1,0 +1,47 @@
+// hybrid_ops.cuh -- launchers of the mechanisms the layer-list decoder (hybrid.cu) is assembled from.  Each returns a b200_status_t.
+#pragma once
+#include "common.cuh"
+
+namespace b200 {
+
+// attention_chunked.cu
+int launch_attn_qk_norm_cache(int dtype, const void *proj, int ld, void *q_out, void *k_pool, void *v_pool, const float *q_norm,
+                              const float *k_norm, float eps, const int *tok_seq, const int *tok_pos, const int *block_table, int mpps,
+                              int tokens, int heads, int kv_heads, int dim, cudaStream_t st);
+int launch_chunked_attention(int dtype, const void *q, const void *k_pool, const void *v_pool, const float *sink, const void *gate_in,
+                             int gate_ld, void *out, const int *tok_seq, const int *tok_pos, const int *block_table, int mpps, int tokens,
+                             int heads, int kv_heads, int dim, float scale, int chunk, int max_keys, cudaStream_t st);
+
+// gla.cu
+// decay[t, c] = sigmoid(z)^(1/tau), z = w_decay[c, :] . proj[t, col0 : col0 + rank] + bias[c]   (fp32 from the projection on)
+int launch_gla_decay(int dtype, const void *proj, int ld, int col0, const void *w_decay, const float *bias, float tau, float *decay,
+                     int tokens, int rank, int channels, cudaStream_t st);
+int launch_gla_recurrent(int dtype, const void *proj, int ld, const float *decay, float *state, float *o, const int *seq_start,
+                         const int *seq_pos0, const int *seq_slot, int n_seqs, int heads, int dim, int vdim, cudaStream_t st);
+// out[t, h*vdim + j] = o[t,h,j] * rsqrt(mean_j o^2 + eps) * w[j] * silu(gate[t*gate_ld + h*vdim + j])
+int launch_gla_output(int dtype, const float *o, const float *w, float eps, const void *gate_in, int gate_ld, void *out, int tokens,
+                      int heads, int vdim, cudaStream_t st);
+
+// moe.cu
+int launch_moe_route_sigmoid(const float *logits, int ld, int *sel_expert, float *sel_weight, float *shared_gate, int tokens,
+                             int experts, int top, cudaStream_t st);
+constexpr int kMoeTileM = 64;  // rows of one expert are padded to whole tiles of this many
+// Groups the (token, choice) pairs by expert.  row_token / row_weight [max_rows]: token of every padded row (-1: padding) and its routing
+// weight; tile_expert [max_tiles]; pair_row [tokens*top]: the row each pair landed in; n_tiles: device int.
+int launch_moe_plan(const int *sel_expert, const float *sel_weight, int *row_token, float *row_weight, int *tile_expert, int *pair_row,
+                    int *n_tiles, int tokens, int experts, int top, int max_rows, cudaStream_t st);
+// xg[row, :] = T(weight[row] * x[token[row], :]) (zeros for padding rows): the routing weight multiplies the expert's INPUT
+int launch_moe_gather(int dtype, const float *x, const int *row_token, const float *row_weight, void *xg, const int *n_tiles,
+                      int max_rows, int width, cudaStream_t st);
+// c[row, n] = act?(sum_k a[row, k] * w[tile_expert[row / kMoeTileM]][n, k]);  rows >= n_tiles * kMoeTileM are skipped
+int launch_moe_grouped_gemm(int dtype, const void *a, const void *w, void *c, const int *tile_expert, const int *n_tiles, int max_tiles,
+                            int N, int K, int act, cudaStream_t st);
+// in place: x = act(x)
+int launch_activation(int dtype, void *x, size_t n, int act, cudaStream_t st);
+
+// hybrid.cu
+// y[m, n] (fp32) = sum_k x[m*ldx + k] * w[n*K + k] (+ bias[n]);  x of type TX (fp32 when x_dtype == B200_F32), w of `w_dtype`
+int launch_proj_f32(int x_dtype, const void *x, int ldx, int w_dtype, const void *w, const float *bias, float *y, int ldy, int M, int N,
+                    int K, cudaStream_t st);
+
+}  // namespace b200

@@ -26,6 +26,7 @@ for FP8 / INT4 packing and for `build_decoder`; everything else is numpy.
 import importlib
 import json
 import os
+import struct
 
 import numpy as np
 
@@ -262,3 +263,33 @@ def build_decoder(packed, shape, device, dtype, wformat, max_seq, max_batch, tp=
     for l, w in enumerate(packed["layers"]):
         dec.set_layer(l, {k: v for k, v in w.items() if v is not None})
     return dec, packed
+
+
+# ------------------------------------------------------------------ safetensors checkpoints
+_ST_DTYPES = {"BF16": ("<u2", "bfloat16"), "F16": ("<f2", "float16"), "F32": ("<f4", "float32"), "I32": ("<i4", "int32"), "I64": ("<i8", "int64")}
+
+
+def read_safetensors(path):
+    """name -> torch CPU tensor.  The format: 8-byte little-endian header length, that many bytes of JSON (name -> dtype, shape,
+    data_offsets), then the raw little-endian data.  bfloat16 is read as 16-bit words and re-viewed, so nothing is converted."""
+    import torch
+
+    with open(path, "rb") as f:
+        (n,) = struct.unpack("<Q", f.read(8))
+        header = json.loads(f.read(n))
+        base = 8 + n
+    data = np.memmap(path, dtype=np.uint8, mode="r", offset=base)
+    out = {}
+    for name, info in header.items():
+        if name == "__metadata__":
+            continue
+        if info["dtype"] not in _ST_DTYPES:
+            raise ValueError(f"{path}: tensor {name} has unsupported dtype {info['dtype']}")
+        np_dt, torch_dt = _ST_DTYPES[info["dtype"]]
+        lo, hi = info["data_offsets"]
+        a = np.frombuffer(data[lo:hi].tobytes(), dtype=np_dt)
+        t = torch.from_numpy(a.copy())
+        if torch_dt == "bfloat16":
+            t = t.view(torch.int16).view(torch.bfloat16)
+        out[name] = t.reshape(info["shape"])
+    return out
