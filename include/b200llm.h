@@ -508,6 +508,13 @@ int b200_chunked_attention_paged(const void *q, const void *k_pool, const void *
                                  int gate_ld, void *out, const int *tok_seq, const int *tok_pos, const int *block_table,
                                  int max_pages_per_seq, int tokens, int heads, int kv_heads, int dim, float scale, int chunk,
                                  int dtype, b200_stream_t stream);
+/* The same attention for prompt portions on the tensor cores (16-bit dtypes, dim 64 or 128; B200_ERR_UNSUPPORTED otherwise).
+ * tiles: DEVICE int[n_tiles][4], 16-byte aligned: {sequence (block-table row), first packed row, rows (1..64), position of the first
+ * row}; the rows of a tile are consecutive tokens of one sequence. */
+int b200_chunked_attention_prefill_paged(const void *q, const void *k_pool, const void *v_pool, const float *sink, const void *gate_in,
+                                         int gate_ld, void *out, const int *tiles, int n_tiles, const int *block_table,
+                                         int max_pages_per_seq, int heads, int kv_heads, int dim, float scale, int chunk, int dtype,
+                                         b200_stream_t stream);
 /* Gated-linear-attention recurrence over every sequence's portion: S <- diag(a_t) S + k_t v_t^T;  o_t = S^T (q_t * dim^-1/2).
  * proj [tokens, ld]: q at column 0, k at heads*dim, v at 2*heads*dim.  decay: fp32 [tokens, heads*dim] (a_t).
  * state: fp32 [num_slots, heads, dim, vdim], read unless the portion starts at position 0, written back at the end.

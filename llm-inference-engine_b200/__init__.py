@@ -181,6 +181,7 @@ SIGNATURES = {
     "b200_hybrid_forward": [_P, C.POINTER(HybridBatch), _P, _P, _P],
     "b200_attn_qk_norm_cache_paged": [_P, _I, _P, _P, _P, _P, _P, _F, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "b200_chunked_attention_paged": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
+    "b200_chunked_attention_prefill_paged": [_P, _P, _P, _P, _P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _F, _I, _I, _P],
     "b200_gla_recurrent": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "b200_moe_route_sigmoid": [_P, _I, _P, _P, _P, _I, _I, _I, _P],
     "b200_batcher_set_state_slots": [_P, _I],
@@ -501,6 +502,59 @@ def context_attention(q, k_cache, v_cache, padding_offset, input_len, context_le
     check(lib().b200_context_attention(ptr(q), ptr(k_cache), ptr(v_cache), ptr(out), ptr(padding_offset), ptr(input_len), ptr(context_len),
                                        layer, B, H, Hkv, mq, S, d, num_tokens, scale, dtype_code(q), stream()))
     return out
+
+
+
+# ---- mechanisms of the layer-list decoder, one wrapper per launcher (see include/b200llm.h)
+def attn_qk_norm_cache_paged(proj, heads, kv_heads, dim, q_norm, k_norm, eps, tok_seq, tok_pos, block_table, k_pool, v_pool):
+    """proj [tokens, >= (heads+kv_heads)*dim] -> q_out [tokens, heads*dim]; appends the keys (normed) and values (keys as projected)."""
+    torch = _torch()
+    q_out = torch.empty((proj.shape[0], heads * dim), dtype=proj.dtype, device=proj.device)
+    check(lib().b200_attn_qk_norm_cache_paged(ptr(proj), proj.shape[1], ptr(q_out), ptr(k_pool), ptr(v_pool), ptr(q_norm), ptr(k_norm), eps,
+                                              ptr(tok_seq), ptr(tok_pos), ptr(block_table), block_table.shape[1], proj.shape[0], heads, kv_heads,
+                                              dim, dtype_code(proj), stream()))
+    return q_out
+
+
+def chunked_attention_paged(q, k_pool, v_pool, sink, gate, tok_seq, tok_pos, block_table, heads, kv_heads, dim, scale, chunk):
+    """q [tokens, heads*dim]; gate (optional) [tokens, heads*dim] pre-sigmoid -> out [tokens, heads*dim]."""
+    torch = _torch()
+    out = torch.empty_like(q)
+    check(lib().b200_chunked_attention_paged(ptr(q), ptr(k_pool), ptr(v_pool), ptr(sink), ptr(gate), gate.shape[1] if gate is not None else 0,
+                                             ptr(out), ptr(tok_seq), ptr(tok_pos), ptr(block_table), block_table.shape[1], q.shape[0], heads,
+                                             kv_heads, dim, scale, chunk, dtype_code(q), stream()))
+    return out
+
+
+def chunked_attention_prefill_paged(q, k_pool, v_pool, sink, gate, tiles, block_table, heads, kv_heads, dim, scale, chunk):
+    """The tensor-core variant for prompt portions.  tiles: int32 [n, 4] device tensor {sequence, first row, rows <= 64, first position}."""
+    torch = _torch()
+    out = torch.zeros_like(q)
+    check(lib().b200_chunked_attention_prefill_paged(ptr(q), ptr(k_pool), ptr(v_pool), ptr(sink), ptr(gate), gate.shape[1] if gate is not None else 0,
+                                                     ptr(out), ptr(tiles), tiles.shape[0], ptr(block_table), block_table.shape[1], heads,
+                                                     kv_heads, dim, scale, chunk, dtype_code(q), stream()))
+    return out
+
+
+def gla_recurrent(proj, decay, state, seq_start, seq_pos0, seq_slot, heads, dim, vdim):
+    """proj [tokens, >= 2*heads*dim + heads*vdim] (q | k | v), decay fp32 [tokens, heads*dim], state fp32 [slots, heads, dim, vdim] (updated)
+    -> o fp32 [tokens, heads*vdim]."""
+    torch = _torch()
+    o = torch.empty((proj.shape[0], heads * vdim), dtype=torch.float32, device=proj.device)
+    check(lib().b200_gla_recurrent(ptr(proj), proj.shape[1], ptr(decay), ptr(state), ptr(o), ptr(seq_start), ptr(seq_pos0), ptr(seq_slot),
+                                   seq_pos0.shape[0], heads, dim, vdim, dtype_code(proj), stream()))
+    return o
+
+
+def moe_route_sigmoid(logits, experts, top, with_shared_gate=True):
+    """logits fp32 [tokens, experts (+1)] -> (chosen int32 [tokens, top], weights fp32 [tokens, top], shared gate fp32 [tokens] or None)."""
+    torch = _torch()
+    n = logits.shape[0]
+    sel = torch.empty((n, top), dtype=torch.int32, device=logits.device)
+    w = torch.empty((n, top), dtype=torch.float32, device=logits.device)
+    gate = torch.empty(n, dtype=torch.float32, device=logits.device) if with_shared_gate else None
+    check(lib().b200_moe_route_sigmoid(ptr(logits), logits.shape[1], ptr(sel), ptr(w), ptr(gate), n, experts, top, stream()))
+    return sel, w, gate
 
 
 class Decoder:

@@ -57,9 +57,9 @@ __global__ void __launch_bounds__(128)
 chunked_attn_kernel(const T *__restrict__ q, const T *__restrict__ k_pool, const T *__restrict__ v_pool, const float *__restrict__ sink,
                     const T *__restrict__ gate_in, int gate_ld, T *__restrict__ out, const int *__restrict__ tok_seq,
                     const int *__restrict__ tok_pos, const int *__restrict__ block_table, int mpps, int heads, int kv_heads, int dim,
-                    float scale, int chunk, int max_keys) {
+                    float scale, int chunk, int max_keys, const int *__restrict__ tok_list) {
     extern __shared__ float sm[];
-    const int t = blockIdx.x, h = blockIdx.y;
+    const int t = tok_list ? tok_list[blockIdx.x] : blockIdx.x, h = blockIdx.y;
     const int g = h / (heads / kv_heads);
     const int pos = tok_pos[t];
     const int first = chunk > 0 ? (pos / chunk) * chunk : 0;
@@ -148,6 +148,238 @@ chunked_attn_kernel(const T *__restrict__ q, const T *__restrict__ k_pool, const
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------------------------
+// Tensor-core prefill kernel (16-bit engines, dim 64 or 128): one CTA = 64 consecutive tokens of ONE sequence x one query head, four
+// warps of 16 rows each.  A key tile is one page (64 positions): K and V arrive by cp.async into a two-stage ring, S = Q K^T and
+// O += P V run on mma.sync.m16n8k16 with fp32 accumulators, the softmax is the online form in fp32.  The sink enters as the INITIAL
+// running state (max = sink, sum = 1, nothing accumulated): exactly a key with that logit and a zero value, and it keeps the running
+// max finite for rows whose first tiles are masked out entirely.  The mask is evaluated per element, so a tile of queries may straddle a
+// chunk edge; the tiles walked are those from the chunk start of the tile's first query to its last query.
+// tiles: int4 per tile {sequence, first packed row, rows (1..64), position of the first row}.
+constexpr int kTileQ = 64;
+
+__device__ __forceinline__ void cp_async16(void *smem, const void *gmem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldsm_x4(unsigned &r0, unsigned &r1, unsigned &r2, unsigned &r3, const void *p) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void ldsm_x4_trans(unsigned &r0, unsigned &r1, unsigned &r2, unsigned &r3, const void *p) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+template <typename T> __device__ __forceinline__ void mma_16816(float *c, const unsigned *a, unsigned b0, unsigned b1);
+template <> __device__ __forceinline__ void mma_16816<__nv_bfloat16>(float *c, const unsigned *a, unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <> __device__ __forceinline__ void mma_16816<__half>(float *c, const unsigned *a, unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <typename T> __device__ __forceinline__ unsigned pack2(float lo, float hi);
+template <> __device__ __forceinline__ unsigned pack2<__nv_bfloat16>(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned *>(&v);
+}
+template <> __device__ __forceinline__ unsigned pack2<__half>(float lo, float hi) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<unsigned *>(&v);
+}
+
+// element (row, col) of a [rows][D] 16-bit tile whose 16-byte pieces are XOR-swizzled by the row: conflict-free ldmatrix
+template <int D> __device__ __forceinline__ int swz(int row, int col) { return row * D + ((((col >> 3) ^ (row & 7)) << 3) | (col & 7)); }
+
+template <typename T, int D>
+__global__ void __launch_bounds__(128)
+chunked_attn_mma_kernel(const T *__restrict__ q, const T *__restrict__ k_pool, const T *__restrict__ v_pool, const float *__restrict__ sink,
+                        const T *__restrict__ gate_in, int gate_ld, T *__restrict__ out, const int4 *__restrict__ tiles,
+                        const int *__restrict__ block_table, int mpps, int heads, int kv_heads, float scale, int chunk) {
+    extern __shared__ __align__(16) unsigned char smraw[];
+    T *qs = reinterpret_cast<T *>(smraw);     // [64][D]
+    T *ks = qs + kTileQ * D;                  // [2][64][D]
+    T *vs = ks + 2 * kPage * D;               // [2][64][D]
+    const int4 tile = tiles[blockIdx.x];
+    const int h = blockIdx.y, g = h / (heads / kv_heads);
+    const int row0 = tile.y, nrows = tile.z, pos0 = tile.w;
+    const int *bt = block_table + (size_t)tile.x * mpps;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
+    constexpr int kPieces = D / 8;            // 16-byte pieces per row
+
+    const int last = pos0 + nrows - 1;
+    const int first = chunk > 0 ? (pos0 / chunk) * chunk : 0;
+    const int tile_lo = first / kPage, tile_hi = last / kPage;
+
+    auto load_kv = [&](int kt, int stage) {
+        const int page = bt[kt];
+        const T *kg = k_pool + ((size_t)page * kv_heads + g) * kPage * D;
+        const T *vg = v_pool + ((size_t)page * kv_heads + g) * kPage * D;
+        for (int i = threadIdx.x; i < kPage * kPieces; i += 128) {
+            const int r = i / kPieces, c = (i % kPieces) * 8;
+            cp_async16(ks + stage * kPage * D + swz<D>(r, c), kg + r * D + c);
+            // rows past the tile's last query have not been written (or belong to a page's previous owner): their probabilities are
+            // zero, but 0 x NaN is NaN on the tensor core, so the values are zeroed rather than fetched
+            if (kt * kPage + r <= last) cp_async16(vs + stage * kPage * D + swz<D>(r, c), vg + r * D + c);
+            else *reinterpret_cast<uint4 *>(vs + stage * kPage * D + swz<D>(r, c)) = make_uint4(0, 0, 0, 0);
+        }
+    };
+    load_kv(tile_lo, 0);
+    cp_async_commit();
+    for (int i = threadIdx.x; i < kTileQ * kPieces; i += 128) {
+        const int r = i / kPieces, c = (i % kPieces) * 8;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < nrows) v = ld_v4(q + ((size_t)(row0 + r) * heads + h) * D + c);
+        *reinterpret_cast<uint4 *>(qs + swz<D>(r, c)) = v;
+    }
+    __syncthreads();
+    unsigned qf[D / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk)
+        ldsm_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], qs + swz<D>(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, kk * 16 + (lane >> 4) * 8));
+
+    constexpr float kLog2e = 1.4426950408889634f;
+    const float sl2 = scale * kLog2e;
+    // rows gid and gid + 8 of this warp's 16
+    const int p_a = pos0 + warp * 16 + gid, p_b = p_a + 8;
+    const int c_a = chunk > 0 ? p_a / chunk : 0, c_b = chunk > 0 ? p_b / chunk : 0;
+    float m_a, m_b, l_a, l_b;
+    if (sink) m_a = m_b = sink[h] * kLog2e, l_a = l_b = tig == 0 ? 1.0f : 0.0f;  // the sum is kept per lane and joined at the end
+    else m_a = m_b = -1e30f, l_a = l_b = 0.0f;
+    float o[D / 8][4];
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
+
+    for (int kt = tile_lo; kt <= tile_hi; ++kt) {
+        const int stage = (kt - tile_lo) & 1;
+        if (kt < tile_hi) load_kv(kt + 1, stage ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const T *kst = ks + stage * kPage * D, *vst = vs + stage * kPage * D;
+        float s[8][4];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+            for (int jp = 0; jp < 4; ++jp) {  // two key blocks of 8 per ldmatrix
+                unsigned b0, b1, b2, b3;
+                ldsm_x4(b0, b1, b2, b3, kst + swz<D>(jp * 16 + (lane & 7) + (lane >> 4) * 8, kk * 16 + ((lane >> 3) & 1) * 8));
+                mma_16816<T>(s[2 * jp], qf[kk], b0, b1);
+                mma_16816<T>(s[2 * jp + 1], qf[kk], b2, b3);
+            }
+        }
+        // scale, mask, running max
+        float mx_a = m_a, mx_b = m_b;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int key = kt * kPage + j * 8 + tig * 2 + e;
+                const int kc = chunk > 0 ? key / chunk : 0;
+                s[j][e] = (key <= p_a && kc == c_a) ? s[j][e] * sl2 : -INFINITY;
+                s[j][2 + e] = (key <= p_b && kc == c_b) ? s[j][2 + e] * sl2 : -INFINITY;
+                mx_a = fmaxf(mx_a, s[j][e]);
+                mx_b = fmaxf(mx_b, s[j][2 + e]);
+            }
+        }
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+        const float f_a = exp2f(m_a - mx_a), f_b = exp2f(m_b - mx_b);
+        m_a = mx_a, m_b = mx_b;
+        float sum_a = 0.0f, sum_b = 0.0f;
+        unsigned pf[4][4];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float e0 = exp2f(s[j][0] - m_a), e1 = exp2f(s[j][1] - m_a), e2 = exp2f(s[j][2] - m_b), e3 = exp2f(s[j][3] - m_b);
+            sum_a += e0 + e1, sum_b += e2 + e3;
+            pf[j >> 1][(j & 1) * 2] = pack2<T>(e0, e1);
+            pf[j >> 1][(j & 1) * 2 + 1] = pack2<T>(e2, e3);
+        }
+        l_a = l_a * f_a + sum_a, l_b = l_b * f_b + sum_b;  // per-lane partial sums; joined across the row's four lanes at the end
+#pragma unroll
+        for (int j = 0; j < D / 8; ++j) o[j][0] *= f_a, o[j][1] *= f_a, o[j][2] *= f_b, o[j][3] *= f_b;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {      // 16 keys per step
+#pragma unroll
+            for (int jp = 0; jp < D / 16; ++jp) {
+                unsigned b0, b1, b2, b3;
+                ldsm_x4_trans(b0, b1, b2, b3, vst + swz<D>(kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, jp * 16 + (lane >> 4) * 8));
+                mma_16816<T>(o[2 * jp], pf[kk], b0, b1);
+                mma_16816<T>(o[2 * jp + 1], pf[kk], b2, b3);
+            }
+        }
+        __syncthreads();  // everybody is done with this stage before the next iteration's prefetch overwrites it
+    }
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+    const float i_a = 1.0f / l_a, i_b = 1.0f / l_b;
+    const int r_a = warp * 16 + gid, r_b = r_a + 8;
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) {
+        const int c = j * 8 + tig * 2;
+        if (r_a < nrows) {
+            float x0 = o[j][0] * i_a, x1 = o[j][1] * i_a;
+            if (gate_in) {
+                const T *gp = gate_in + (size_t)(row0 + r_a) * gate_ld + h * D + c;
+                x0 *= 1.0f / (1.0f + expf(-Elem<T>::to_f(gp[0]))), x1 *= 1.0f / (1.0f + expf(-Elem<T>::to_f(gp[1])));
+            }
+            *reinterpret_cast<unsigned *>(out + ((size_t)(row0 + r_a) * heads + h) * D + c) = pack2<T>(x0, x1);
+        }
+        if (r_b < nrows) {
+            float x2 = o[j][2] * i_b, x3 = o[j][3] * i_b;
+            if (gate_in) {
+                const T *gp = gate_in + (size_t)(row0 + r_b) * gate_ld + h * D + c;
+                x2 *= 1.0f / (1.0f + expf(-Elem<T>::to_f(gp[0]))), x3 *= 1.0f / (1.0f + expf(-Elem<T>::to_f(gp[1])));
+            }
+            *reinterpret_cast<unsigned *>(out + ((size_t)(row0 + r_b) * heads + h) * D + c) = pack2<T>(x2, x3);
+        }
+    }
+}
+
+template <typename T, int D>
+static int launch_mma_t(const void *q, const void *k_pool, const void *v_pool, const float *sink, const void *gate_in, int gate_ld, void *out,
+                        const int *tiles, int n_tiles, const int *block_table, int mpps, int heads, int kv_heads, float scale, int chunk,
+                        cudaStream_t st) {
+    const size_t smem = (size_t)(kTileQ + 4 * kPage) * D * sizeof(T);
+    cudaFuncSetAttribute(chunked_attn_mma_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    chunked_attn_mma_kernel<T, D><<<dim3(n_tiles, heads), 128, smem, st>>>((const T *)q, (const T *)k_pool, (const T *)v_pool, sink, (const T *)gate_in,
+                                                                            gate_ld, (T *)out, (const int4 *)tiles, block_table, mpps, heads, kv_heads,
+                                                                            scale, chunk);
+    return cuda_status("chunked_attention (tensor core) launch");
+}
+
+bool chunked_attention_tiles_supported(int dtype, int dim, int gate_ld) {
+    return dtype != B200_F32 && (dim == 64 || dim == 128) && gate_ld % 2 == 0;
+}
+
+int launch_chunked_attention_tiles(int dtype, const void *q, const void *k_pool, const void *v_pool, const float *sink, const void *gate_in,
+                                   int gate_ld, void *out, const int *tiles, int n_tiles, const int *block_table, int mpps, int heads,
+                                   int kv_heads, int dim, float scale, int chunk, cudaStream_t st) {
+    if (n_tiles == 0) return B200_OK;
+    if (!chunked_attention_tiles_supported(dtype, dim, gate_ld)) {
+        set_error("chunked_attention tiles: 16-bit dtypes and dim 64 / 128 only");
+        return B200_ERR_UNSUPPORTED;
+    }
+#define B200_ATTN_TILES(TT, DD) \
+    return launch_mma_t<TT, DD>(q, k_pool, v_pool, sink, gate_in, gate_ld, out, tiles, n_tiles, block_table, mpps, heads, kv_heads, scale, chunk, st)
+    if (dtype == B200_BF16) {
+        if (dim == 64) B200_ATTN_TILES(__nv_bfloat16, 64);
+        B200_ATTN_TILES(__nv_bfloat16, 128);
+    }
+    if (dim == 64) B200_ATTN_TILES(__half, 64);
+    B200_ATTN_TILES(__half, 128);
+#undef B200_ATTN_TILES
+}
+
 int launch_attn_qk_norm_cache(int dtype, const void *proj, int ld, void *q_out, void *k_pool, void *v_pool, const float *q_norm,
                               const float *k_norm, float eps, const int *tok_seq, const int *tok_pos, const int *block_table, int mpps,
                               int tokens, int heads, int kv_heads, int dim, cudaStream_t st) {
@@ -161,7 +393,7 @@ int launch_attn_qk_norm_cache(int dtype, const void *proj, int ld, void *q_out, 
 
 int launch_chunked_attention(int dtype, const void *q, const void *k_pool, const void *v_pool, const float *sink, const void *gate_in,
                              int gate_ld, void *out, const int *tok_seq, const int *tok_pos, const int *block_table, int mpps, int tokens,
-                             int heads, int kv_heads, int dim, float scale, int chunk, int max_keys, cudaStream_t st) {
+                             int heads, int kv_heads, int dim, float scale, int chunk, int max_keys, cudaStream_t st, const int *tok_list) {
     if (tokens == 0) return B200_OK;
     const int threads = 128;
     const int ngroups = threads >= dim ? threads / dim : 1;
@@ -174,7 +406,7 @@ int launch_chunked_attention(int dtype, const void *q, const void *k_pool, const
         if (smem > 48 * 1024) cudaFuncSetAttribute(chunked_attn_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         chunked_attn_kernel<T><<<dim3(tokens, heads), threads, smem, st>>>((const T *)q, (const T *)k_pool, (const T *)v_pool, sink,
                                                                             (const T *)gate_in, gate_ld, (T *)out, tok_seq, tok_pos,
-                                                                            block_table, mpps, heads, kv_heads, dim, scale, chunk, max_keys);
+                                                                            block_table, mpps, heads, kv_heads, dim, scale, chunk, max_keys, tok_list);
     });
     return cuda_status("chunked_attention launch");
 }
@@ -202,6 +434,17 @@ int b200_chunked_attention_paged(const void *q, const void *k_pool, const void *
     B200_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dim > 0 && chunk >= 0, "chunked_attention: bad shape");
     const int max_keys = chunk > 0 ? chunk : max_pages_per_seq * kPage;
     return launch_chunked_attention(dtype, q, k_pool, v_pool, sink, gate_in, gate_ld, out, tok_seq, tok_pos, block_table,
-                                    max_pages_per_seq, tokens, heads, kv_heads, dim, scale, chunk, max_keys, as_stream(stream));
+                                    max_pages_per_seq, tokens, heads, kv_heads, dim, scale, chunk, max_keys, as_stream(stream), nullptr);
+}
+
+int b200_chunked_attention_prefill_paged(const void *q, const void *k_pool, const void *v_pool, const float *sink, const void *gate_in,
+                                         int gate_ld, void *out, const int *tiles, int n_tiles, const int *block_table,
+                                         int max_pages_per_seq, int heads, int kv_heads, int dim, float scale, int chunk, int dtype,
+                                         b200_stream_t stream) {
+    B200_REQUIRE(q && k_pool && v_pool && out && tiles && block_table, "chunked_attention_prefill: null pointer");
+    B200_REQUIRE(n_tiles >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && chunk >= 0, "chunked_attention_prefill: bad shape");
+    B200_REQUIRE(((uintptr_t)tiles & 15) == 0, "chunked_attention_prefill: the tile list must be 16-byte aligned");
+    return launch_chunked_attention_tiles(dtype, q, k_pool, v_pool, sink, gate_in, gate_ld, out, tiles, n_tiles, block_table, max_pages_per_seq,
+                                          heads, kv_heads, dim, scale, chunk, as_stream(stream));
 }
 }

@@ -194,8 +194,9 @@ Carve carve(const b200_hybrid *m) {
     k.yrows = align256(rows * c.width * es);
     k.us = align256(T * sff * es);
     k.ys = align256(T * c.width * es);
-    // meta: ids | tok_seq | tok_pos | want [T each] | seq_start [S+1] | pos0 | slot [S each] | block table [S * mpps]
-    k.meta = align256((4 * T + 3 * (size_t)c.max_seqs + 1 + (size_t)c.max_seqs * c.max_pages_per_seq) * 4);
+    // meta: attention tiles [4 * (T/64 + S), padded] | ids | tok_seq | tok_pos | want | short-portion token list [T each] | seq_start [S+1] |
+    //       pos0 | slot [S each] | block table [S * mpps]
+    k.meta = align256((4 * (T / 64 + (size_t)c.max_seqs + 1) + 5 * T + 3 * (size_t)c.max_seqs + 1 + (size_t)c.max_seqs * c.max_pages_per_seq) * 4);
     // moe ints: sel_expert | pair_row [T*top each] | row_token [rows] | tile_expert [rows / tile] | n_tiles
     k.moe_i = align256((2 * T * top + rows + rows / kMoeTileM + 4) * 4);
     // moe floats: sel_weight [T*top] | row_weight [rows] | shared_gate [T]
@@ -347,9 +348,13 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
 
     // ---- batch description: checked on the host, shipped in one copy
     std::vector<int> &hm = m->host_meta;
-    hm.assign((size_t)4 * NT + 3 * S + 1 + (size_t)S * mpps, 0);
-    int *h_ids = hm.data(), *h_seq = h_ids + NT, *h_pos = h_seq + NT, *h_want = h_pos + NT, *h_start = h_want + NT, *h_pos0 = h_start + S + 1,
-        *h_slot = h_pos0 + S, *h_bt = h_slot + S;
+    const size_t n_tile_ints = 4 * ((size_t)NT / 64 + S + 1);
+    hm.assign(n_tile_ints + (size_t)5 * NT + 3 * S + 1 + (size_t)S * mpps, 0);
+    int *h_tiles = hm.data(), *h_ids = h_tiles + n_tile_ints, *h_seq = h_ids + NT, *h_pos = h_seq + NT, *h_want = h_pos + NT, *h_short = h_want + NT,
+        *h_start = h_short + NT, *h_pos0 = h_start + S + 1, *h_slot = h_pos0 + S, *h_bt = h_slot + S;
+    // prompt portions go to the tensor-core attention in tiles of <= 64 consecutive tokens, short ones (decoded tokens) to the per-token kernel
+    constexpr int kShortPortion = 8;
+    int n_tiles = 0, n_short = 0;
     for (int s = 0; s < S; ++s) {
         const int t0 = b->seq_start[s], t1 = b->seq_start[s + 1];
         B200_REQUIRE(t1 >= t0 && b->seq_pos0[s] >= 0, "hybrid_forward: bad portion of sequence %d", s);
@@ -362,6 +367,14 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
             B200_REQUIRE(page >= 0 && page < m->num_pages, "hybrid_forward: sequence %d holds no page for positions %d..", s, p * kPageH);
         }
         for (int t = t0; t < t1; ++t) h_seq[t] = s, h_pos[t] = b->seq_pos0[s] + (t - t0);
+        if (t1 - t0 < kShortPortion) {
+            for (int t = t0; t < t1; ++t) h_short[n_short++] = t;
+        } else {
+            for (int t = t0; t < t1; t += 64, ++n_tiles) {
+                int *tl = h_tiles + 4 * n_tiles;
+                tl[0] = s, tl[1] = t, tl[2] = std::min(64, t1 - t), tl[3] = h_pos[t];
+            }
+        }
         h_start[s] = t0, h_pos0[s] = b->seq_pos0[s], h_slot[s] = b->seq_slot[s];
         for (int p = 0; p < mpps; ++p) h_bt[(size_t)s * mpps + p] = b->block_table[(size_t)s * mpps + p];
     }
@@ -377,8 +390,8 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
     cudaStream_t st = as_stream(stream);
     NvtxRange range("hybrid_forward");
     if (cudaMemcpyAsync(m->meta, hm.data(), hm.size() * sizeof(int), cudaMemcpyHostToDevice, st) != cudaSuccess) return cuda_status("hybrid_forward meta copy");
-    const int *d_ids = m->meta, *d_seq = d_ids + NT, *d_pos = d_seq + NT, *d_want = d_pos + NT, *d_start = d_want + NT, *d_pos0 = d_start + S + 1,
-              *d_slot = d_pos0 + S, *d_bt = d_slot + S;
+    const int *d_tiles = m->meta, *d_ids = d_tiles + n_tile_ints, *d_seq = d_ids + NT, *d_pos = d_seq + NT, *d_want = d_pos + NT, *d_short = d_want + NT,
+              *d_start = d_short + NT, *d_pos0 = d_start + S + 1, *d_slot = d_pos0 + S, *d_bt = d_slot + S;
 
     const int dt = c.dtype, width = c.width;
     const bool f32 = dt == B200_F32;
@@ -418,8 +431,15 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
             RUN(launch_attn_qk_norm_cache(dt, m->proj, lp.n_in, m->mix, m->kv_pool + lp.k_off, m->kv_pool + lp.v_off, l.q_norm, l.k_norm, c.norm_eps,
                                           d_seq, d_pos, d_bt, mpps, NT, l.heads, l.kv_heads, l.dim, st));
             const int max_keys = l.chunk > 0 ? l.chunk : mpps * kPageH;
-            RUN(launch_chunked_attention(dt, m->mix, m->kv_pool + lp.k_off, m->kv_pool + lp.v_off, l.sink, gate, lp.n_in, m->mix2, d_seq, d_pos,
-                                         d_bt, mpps, NT, l.heads, l.kv_heads, l.dim, l.scale, l.chunk, max_keys, st));
+            if (chunked_attention_tiles_supported(dt, l.dim, lp.n_in)) {
+                RUN(launch_chunked_attention_tiles(dt, m->mix, m->kv_pool + lp.k_off, m->kv_pool + lp.v_off, l.sink, gate, lp.n_in, m->mix2, d_tiles,
+                                                   n_tiles, d_bt, mpps, l.heads, l.kv_heads, l.dim, l.scale, l.chunk, st));
+                RUN(launch_chunked_attention(dt, m->mix, m->kv_pool + lp.k_off, m->kv_pool + lp.v_off, l.sink, gate, lp.n_in, m->mix2, d_seq, d_pos,
+                                             d_bt, mpps, n_short, l.heads, l.kv_heads, l.dim, l.scale, l.chunk, max_keys, st, d_short));
+            } else {
+                RUN(launch_chunked_attention(dt, m->mix, m->kv_pool + lp.k_off, m->kv_pool + lp.v_off, l.sink, gate, lp.n_in, m->mix2, d_seq, d_pos,
+                                             d_bt, mpps, NT, l.heads, l.kv_heads, l.dim, l.scale, l.chunk, max_keys, st));
+            }
             RUN(linear(m, m->mix2, l.w_out, m->y, NT, hd, width, st));
         } else {
             const int hd = l.heads * l.dim, hv = l.heads * l.vdim;

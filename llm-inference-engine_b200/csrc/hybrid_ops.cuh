@@ -10,7 +10,12 @@ int launch_attn_qk_norm_cache(int dtype, const void *proj, int ld, void *q_out, 
                               int tokens, int heads, int kv_heads, int dim, cudaStream_t st);
 int launch_chunked_attention(int dtype, const void *q, const void *k_pool, const void *v_pool, const float *sink, const void *gate_in,
                              int gate_ld, void *out, const int *tok_seq, const int *tok_pos, const int *block_table, int mpps, int tokens,
-                             int heads, int kv_heads, int dim, float scale, int chunk, int max_keys, cudaStream_t st);
+                             int heads, int kv_heads, int dim, float scale, int chunk, int max_keys, cudaStream_t st, const int *tok_list = nullptr);
+// tensor-core prefill variant over tiles of <= 64 consecutive tokens of one sequence: int4 {sequence, first packed row, rows, first position}
+bool chunked_attention_tiles_supported(int dtype, int dim, int gate_ld);
+int launch_chunked_attention_tiles(int dtype, const void *q, const void *k_pool, const void *v_pool, const float *sink, const void *gate_in,
+                                   int gate_ld, void *out, const int *tiles, int n_tiles, const int *block_table, int mpps, int heads,
+                                   int kv_heads, int dim, float scale, int chunk, cudaStream_t st);
 
 // gla.cu
 // decay[t, c] = sigmoid(z)^(1/tau), z = w_decay[c, :] . proj[t, col0 : col0 + rank] + bias[c]   (fp32 from the projection on)

@@ -142,6 +142,100 @@ moe_grouped_gemm_kernel(const T *__restrict__ a, const T *__restrict__ w, T *__r
         }
 }
 
+// Tensor-core grouped GEMM for 16-bit engines (K a multiple of 8): CTA tile 64 rows (one expert's tile) x 128 columns, K in steps of 64
+// through a three-stage cp.async ring, four warps of 32 x 64 on mma.sync.m16n8k16, fp32 accumulators, activation in the epilogue.
+constexpr int kMN = 128, kMK = 64, kMStages = 3;
+__device__ __forceinline__ void moe_cp16(void *smem, const void *gmem, bool live) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    const int n = live ? 16 : 0;  // src-size 0: the 16 bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(n) : "memory");
+}
+__device__ __forceinline__ int moe_swz(int row, int col) { return row * kMK + ((((col >> 3) ^ (row & 7)) << 3) | (col & 7)); }
+template <typename T> __device__ __forceinline__ void moe_mma(float *c, const unsigned *a, unsigned b0, unsigned b1);
+template <> __device__ __forceinline__ void moe_mma<__nv_bfloat16>(float *c, const unsigned *a, unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <> __device__ __forceinline__ void moe_mma<__half>(float *c, const unsigned *a, unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void moe_ldsm(unsigned &r0, unsigned &r1, unsigned &r2, unsigned &r3, const void *p) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_grouped_gemm_mma_kernel(const T *__restrict__ a, const T *__restrict__ w, T *__restrict__ c, const int *__restrict__ tile_expert,
+                            const int *__restrict__ n_tiles, int N, int K, int act) {
+    if ((int)blockIdx.y >= *n_tiles) return;
+    extern __shared__ __align__(16) unsigned char smraw[];
+    T *As = reinterpret_cast<T *>(smraw);               // [stages][64][64]
+    T *Bs = As + kMStages * kMoeTileM * kMK;            // [stages][128][64]
+    const int m0 = blockIdx.y * kMoeTileM, n0 = blockIdx.x * kMN;
+    const T *wb = w + (size_t)tile_expert[blockIdx.y] * N * K;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
+    const int wm = warp >> 1, wn = warp & 1;
+    const int nk = (K + kMK - 1) / kMK;
+    auto load = [&](int kt, int stage) {
+        const int k0 = kt * kMK;
+        T *as = As + stage * kMoeTileM * kMK, *bs = Bs + stage * kMN * kMK;
+        for (int i = threadIdx.x; i < kMoeTileM * 8; i += 128) {
+            const int r = i >> 3, cc = (i & 7) * 8;
+            const bool live = k0 + cc < K;
+            moe_cp16(as + moe_swz(r, cc), a + (size_t)(m0 + r) * K + (live ? k0 + cc : 0), live);
+        }
+        for (int i = threadIdx.x; i < kMN * 8; i += 128) {
+            const int r = i >> 3, cc = (i & 7) * 8;
+            const bool live = k0 + cc < K && n0 + r < N;
+            moe_cp16(bs + moe_swz(r, cc), wb + (live ? (size_t)(n0 + r) * K + k0 + cc : 0), live);
+        }
+    };
+    for (int s = 0; s < kMStages - 1; ++s) {
+        if (s < nk) load(s, s);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    float acc[2][8][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.0f;
+    for (int kt = 0; kt < nk; ++kt) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(kMStages - 2) : "memory");
+        __syncthreads();
+        if (kt + kMStages - 1 < nk) load(kt + kMStages - 1, (kt + kMStages - 1) % kMStages);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        const T *as = As + (kt % kMStages) * kMoeTileM * kMK, *bs = Bs + (kt % kMStages) * kMN * kMK;
+#pragma unroll
+        for (int kk = 0; kk < kMK / 16; ++kk) {
+            unsigned af[2][4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+                moe_ldsm(af[i][0], af[i][1], af[i][2], af[i][3], as + moe_swz(wm * 32 + i * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, kk * 16 + (lane >> 4) * 8));
+#pragma unroll
+            for (int jp = 0; jp < 4; ++jp) {
+                unsigned b0, b1, b2, b3;
+                moe_ldsm(b0, b1, b2, b3, bs + moe_swz(wn * 64 + jp * 16 + (lane & 7) + (lane >> 4) * 8, kk * 16 + ((lane >> 3) & 1) * 8));
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    moe_mma<T>(acc[i][2 * jp], af[i], b0, b1);
+                    moe_mma<T>(acc[i][2 * jp + 1], af[i], b2, b3);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int m = m0 + wm * 32 + i * 16 + gid + (e >> 1) * 8, n = n0 + wn * 64 + j * 8 + tig * 2 + (e & 1);
+                if (n < N) c[(size_t)m * N + n] = Elem<T>::from_f(act >= 0 ? act_apply(acc[i][j][e], act) : acc[i][j][e]);
+            }
+}
+
 template <typename T>
 __global__ void activation_kernel(T *__restrict__ x, size_t n, int act) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -173,6 +267,19 @@ int launch_moe_gather(int dtype, const float *x, const int *row_token, const flo
 int launch_moe_grouped_gemm(int dtype, const void *a, const void *w, void *c, const int *tile_expert, const int *n_tiles, int max_tiles,
                             int N, int K, int act, cudaStream_t st) {
     if (max_tiles == 0) return B200_OK;
+    if (dtype != B200_F32 && K % 8 == 0) {
+        const dim3 grid((N + kMN - 1) / kMN, max_tiles);
+        const size_t smem = (size_t)kMStages * (kMoeTileM + kMN) * kMK * 2;
+        if (dtype == B200_BF16) {
+            cudaFuncSetAttribute(moe_grouped_gemm_mma_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            moe_grouped_gemm_mma_kernel<__nv_bfloat16><<<grid, 128, smem, st>>>((const __nv_bfloat16 *)a, (const __nv_bfloat16 *)w, (__nv_bfloat16 *)c,
+                                                                                tile_expert, n_tiles, N, K, act);
+        } else {
+            cudaFuncSetAttribute(moe_grouped_gemm_mma_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            moe_grouped_gemm_mma_kernel<__half><<<grid, 128, smem, st>>>((const __half *)a, (const __half *)w, (__half *)c, tile_expert, n_tiles, N, K, act);
+        }
+        return cuda_status("moe_grouped_gemm (tensor core) launch");
+    }
     const dim3 grid((N + kGT - 1) / kGT, max_tiles);
     B200_DISPATCH_DTYPE(dtype, {
         moe_grouped_gemm_kernel<T><<<grid, 256, 0, st>>>((const T *)a, (const T *)w, (T *)c, tile_expert, n_tiles, N, K, act);
