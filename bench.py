@@ -46,6 +46,20 @@ CONFIGS = {
     # diagnostics: ONE rank's shard of the 70B-shaped model under TP-8, run on one GPU without the exchange (kernel-level profiling)
     "70b-tp8-rank": dict(name="Llama-2-70B-shaped, one TP-8 shard", hidden=8192, head_num=8, kv_head_num=1, head_size=128, inter=3584, layers=80, vocab=32000),
 }
+# Llama-shaped models of the same width, depth and active parameters as the --mode hybrid sizes (the closest dense model, for side-by-side numbers)
+CONFIGS.update({
+    "hybrid-s-like": dict(name="dense model at hybrid size s", hidden=1024, head_num=8, kv_head_num=2, head_size=128, inter=1408, layers=4, vocab=32000),
+    "hybrid-m-like": dict(name="dense model at hybrid size m", hidden=2048, head_num=16, kv_head_num=4, head_size=128, inter=2688, layers=4, vocab=32000),
+    "hybrid-l-like": dict(name="dense model at hybrid size l", hidden=4096, head_num=32, kv_head_num=8, head_size=128, inter=5504, layers=4, vocab=32000),
+})
+HYBRID_SIZES = {  # Vasolix-shaped layer lists (gla, attention, gla, attention; every layer with a mixture of experts), random weights
+    "s": dict(width=1024, attn=dict(heads=8, kv_heads=2, dim=128, chunk=512), gla=dict(heads=4, dim=64, vdim=256, rank=32),
+              moe=dict(experts=16, top=2, ff=512, shared=1024)),
+    "m": dict(width=2048, attn=dict(heads=16, kv_heads=4, dim=128, chunk=1024), gla=dict(heads=8, dim=128, vdim=256, rank=64),
+              moe=dict(experts=32, top=4, ff=512, shared=2048)),
+    "l": dict(width=4096, attn=dict(heads=32, kv_heads=8, dim=128, chunk=2048), gla=dict(heads=16, dim=128, vdim=256, rank=64),
+              moe=dict(experts=64, top=4, ff=1024, shared=4096)),
+}
 WBYTES = {"bf16": 2.0, "fp8": 1.0, "int4": 0.5}
 
 
@@ -704,6 +718,117 @@ def workload_config(args, cfg):
             "cache_policy": "inputs larger than L2 (13.7 GB of weights + KV per step vs 126 MB L2); no explicit flush"}
 
 
+def run_hybrid(args):
+    """--mode hybrid: prefill and decode throughput of a Vasolix-shaped model (random weights, bf16) on the layer-list decoder, at one of
+    HYBRID_SIZES.  Prefill: one prompt of --prefill-tokens tokens in one engine call.  Decode: --batch sequences with --ctx cached positions
+    each, one token per sequence per step, through the same call a served request takes (host batch description in, device logits out).
+    The dense model of equal width / depth / active parameters is CONFIGS['hybrid-<size>-like'] under --mode prefill and the default mode."""
+    import numpy as np
+    import torch
+
+    mod = importlib.import_module("llm-inference-engine_b200")
+    mod.lib()
+    vas = importlib.import_module("llm-inference-engine_b200.models.vasolix")
+    sz = HYBRID_SIZES[args.hybrid_size]
+    W, A, G, M, V = sz["width"], sz["attn"], sz["gla"], sz["moe"], 32000
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    mlp = {"kind": "moe", "expert": {"ff": M["ff"]}, "router": {"experts": M["experts"], "top": M["top"]}, "shared": {"ff": M["shared"]}}
+    gla = {"type": "gla", "mixer": {"heads": G["heads"], "dim": G["dim"], "vdim": G["vdim"], "tau": 16.0}, "mlp": mlp}
+    att = {"type": "attention", "mixer": {"heads": A["heads"], "kv_heads": A["kv_heads"], "dim": A["dim"], "vdim": A["dim"], "scale": A["dim"] ** -0.5,
+                                          "mask": {"size": A["chunk"]}}, "mlp": mlp}
+    config = {"architecture": "Vasolix", "layers": [gla, att, gla, att], "norm": {"eps": 1e-6}, "vocab": V, "width": W}
+    gen = torch.Generator().manual_seed(7)
+
+    def rnd(*shape, std=0.02):
+        return (torch.randn(*shape, generator=gen) * std).to(torch.bfloat16)
+
+    t = {"embed": rnd(V, W, std=1.0), "head": rnd(V, W), "final.norm": torch.ones(W, dtype=torch.bfloat16)}
+    for i, layer in enumerate(config["layers"]):
+        p, mx = f"l{i}.", layer["mixer"]
+        H, d = mx["heads"], mx["dim"]
+        t[p + "norm1"], t[p + "norm2"] = torch.ones(W, dtype=torch.bfloat16), torch.ones(W, dtype=torch.bfloat16)
+        if layer["type"] == "attention":
+            Gk = mx["kv_heads"]
+            t.update({p + "mix.q": rnd(H * d, W), p + "mix.k": rnd(Gk * d, W), p + "mix.g": rnd(H * d, W), p + "mix.o": rnd(W, H * d),
+                      p + "mix.q.norm": torch.ones(H * d, dtype=torch.bfloat16), p + "mix.k.norm": torch.ones(Gk * d, dtype=torch.bfloat16),
+                      p + "mix.sink": torch.zeros(H, dtype=torch.bfloat16)})
+        else:
+            dv, r = mx["vdim"], G["rank"]
+            t.update({p + "mix.q": rnd(H * d, W), p + "mix.k": rnd(H * d, W), p + "mix.v": rnd(H * dv, W), p + "mix.g": rnd(H * dv, W),
+                      p + "mix.o": rnd(W, H * dv), p + "mix.a1": rnd(r, W), p + "mix.a2": rnd(H * d, r), p + "mix.a2.b": torch.full((H * d,), 3.0).to(torch.bfloat16),
+                      p + "mix.norm": torch.ones(dv, dtype=torch.bfloat16)})
+        t[p + "mlp.router"] = rnd(M["experts"], W)
+        up, down = rnd(M["experts"], M["ff"], W), rnd(M["experts"], W, M["ff"])
+        for e in range(M["experts"]):
+            t[f"{p}mlp.e{e}.up"], t[f"{p}mlp.e{e}.down"] = up[e], down[e]
+        t.update({p + "mlp.shared.up": rnd(M["shared"], W), p + "mlp.shared.down": rnd(W, M["shared"]), p + "mlp.shared.sg": rnd(1, W)})
+    Tq, B, ctx = args.prefill_tokens, args.batch, args.ctx
+    page = mod.KV_PAGE_SIZE
+    per_seq = (max(Tq, ctx + args.steps + args.warmup + 8) + page - 1) // page
+    model = vas.VasolixModel(config, t, dtype="bfloat16", device=dev, max_tokens=max(Tq, B, 2048), max_seqs=max(B, 1), max_pages_per_seq=per_seq)
+    eng = model.engine
+    eng.set_pools(per_seq * max(B, 1), max(B, 1))
+    ids = torch.randint(0, V, (max(Tq, ctx + 1),), generator=gen).tolist()
+    bt = np.arange(per_seq * max(B, 1), dtype=np.int32).reshape(max(B, 1), per_seq)
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    # active parameters per token and layer pair (one gla + one attention layer), matrices only
+    moe_p = 2 * W * (M["top"] * M["ff"] + M["shared"]) + W * (M["experts"] + 1)
+    att_p = W * (2 * A["heads"] + A["kv_heads"]) * A["dim"] + A["heads"] * A["dim"] * W
+    gla_p = W * (2 * G["heads"] * G["dim"] + 2 * G["heads"] * G["vdim"] + G["rank"]) + G["rank"] * G["heads"] * G["dim"] + G["heads"] * G["vdim"] * W
+    active = 2 * (moe_p * 2 + att_p + gla_p)
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(0, gpu_uuid(dev)) as clocks:
+            e0.record()
+            for _ in range(steps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps, clocks.summary()
+
+    # ---- prefill: one sequence, Tq tokens, one call (the pass recomputes from position 0 every time: state and pages are overwritten)
+    pre_ms, pre_clocks = timed(lambda: eng.forward(ids[:Tq], [0, Tq], [0], [0], bt[:1].reshape(-1), [Tq - 1]), max(3, min(args.steps, 20)), 3)
+    chunk = A["chunk"]
+    attn_flops = 2 * 4.0 * A["heads"] * A["dim"] * sum(min(i % chunk, chunk) + 1 for i in range(Tq))
+    gla_flops = 2 * 4.0 * G["heads"] * G["dim"] * G["vdim"] * Tq
+    pre_tflops = (2.0 * Tq * active + attn_flops + gla_flops) / (pre_ms * 1e-3) / 1e12
+    # ---- decode: B sequences with ctx cached positions (filled by a prefill each), then one token each per step
+    for b in range(B):
+        eng.forward(ids[:ctx], [0, ctx], [0], [b], bt[b:b + 1].reshape(-1), [])
+    state = {"pos": ctx}
+
+    def step():
+        eng.forward(ids[:B], list(range(B + 1)), [state["pos"]] * B, list(range(B)), bt.reshape(-1), list(range(B)))
+        state["pos"] += 1
+
+    dec_ms, dec_clocks = timed(step, args.steps, max(args.warmup, 3))
+    es = 2
+    touched = min(M["experts"], B * M["top"])
+    w_bytes = es * 2 * ((att_p + gla_p) + 2 * (2 * W * (touched * M["ff"] + M["shared"]) + W * (M["experts"] + 1))) + es * V * W
+    kv_bytes = 2 * es * 2 * B * A["kv_heads"] * A["dim"] * min(ctx % chunk + 1, chunk) * 1.0
+    st_bytes = 2 * 4 * 2 * B * G["heads"] * G["dim"] * G["vdim"]
+    dec_gbs = (w_bytes + kv_bytes + st_bytes) / (dec_ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "hybrid prefill / decode tokens/s", "value": Tq * 1e3 / pre_ms, "unit": "tokens/s (prefill)", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "higher_is_better": True, "dtype": "bf16", "data": "synthetic", "impl": "b200",
+        "config": {"model": f"Vasolix-shaped, size {args.hybrid_size}: width {W}, 4 layers (gla, attention, gla, attention), {M['experts']} experts top {M['top']}",
+                   "prefill_tokens": Tq, "decode_batch": B, "decode_context": ctx, "cache_policy": "weights larger than L2 at sizes m and l; no explicit flush"},
+        "prefill": {"tokens_per_s": Tq * 1e3 / pre_ms, "ms": pre_ms, "tflops": pre_tflops,
+                    "frac_of_measured_bf16_sustained": pre_tflops / float(peaks.get("bf16_tflops_sustained", 1400.0)), "clocks": pre_clocks},
+        "decode": {"tokens_per_s": B * 1e3 / dec_ms, "ms_per_step": dec_ms, "algorithmic_gb_per_s": dec_gbs,
+                   "frac_of_measured_hbm": dec_gbs / float(peaks.get("hbm_gbs", 6650.0)), "clocks": dec_clocks},
+        "e2e": "both numbers are taken through HybridDecoder.forward: host batch description in (one H2D copy per call), device logits out"}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -716,7 +841,8 @@ def main():
     ap.add_argument("--wformat", default="bf16", choices=list(WBYTES))
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (debug only: makes the number INVALID)")
     ap.add_argument("--requests", type=int, default=64, help="--mode serve: requests in the stream (prompts of 32..512, 32..256 new tokens)")
-    ap.add_argument("--mode", default="decode", choices=["decode", "prefill", "generate", "serve"],
+    ap.add_argument("--hybrid-size", default="m", choices=list(HYBRID_SIZES), help="--mode hybrid: which Vasolix-shaped model")
+    ap.add_argument("--mode", default="decode", choices=["decode", "prefill", "generate", "serve", "hybrid"],
                     help="decode (default, the BASELINE metric); prefill: one pass of --prefill-tokens tokens through all layers; generate: "
                          "the whole loop through b200_generate (prompt of --prefill-tokens tokens, --new-tokens sampled tokens, host in / host out)")
     ap.add_argument("--new-tokens", type=int, default=128)
@@ -742,6 +868,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, cfg, rank)
+        return
+    if args.mode == "hybrid":
+        run_hybrid(args)
         return
     if args.cpu_leg:  # child process of the product arm: the only place of that arm where oracle/ is loaded
         run_cpu_leg(args, cfg)

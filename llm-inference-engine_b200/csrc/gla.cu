@@ -86,6 +86,107 @@ gla_recurrent_kernel(const T *__restrict__ proj, int ld, const float *__restrict
         for (int i = rg; i < dim; i += kRowGroups) slot[(size_t)i * vdim + j0 + col] = S[i * kGlaCols + col];
 }
 
+// Register-resident variant (dim <= 4 * R): the tile of S lives in registers, R rows per thread.  A warp owns 8 columns; its lanes are
+// 8 columns x 4 row groups (rows rg, rg + 4, ...), so the sum over rows ends with two shuffles and no barrier.  Tokens are staged in
+// blocks of TB: {decay, k, q} of a row as one float4 in shared memory (one 16-byte broadcast load per row and token), the next block's
+// global loads are issued before the current block is computed.  One barrier pair per TB tokens.
+template <typename T, int R, int TB>
+__global__ void __launch_bounds__(128)
+gla_recurrent_reg_kernel(const T *__restrict__ proj, int ld, const float *__restrict__ decay, float *__restrict__ state, float *__restrict__ o,
+                         const int *__restrict__ seq_start, const int *__restrict__ seq_pos0, const int *__restrict__ seq_slot, int heads,
+                         int dim, int vdim) {
+    extern __shared__ __align__(16) float smf[];
+    float4 *akq = reinterpret_cast<float4 *>(smf);              // [TB][dim]
+    float *vs = smf + (size_t)TB * dim * 4;                      // [TB][32]
+    constexpr int E = TB * R / 32;                               // staged (row, token) pairs per thread
+    const int j0 = blockIdx.x * kGlaCols, h = blockIdx.y, s = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, cg = lane & 7, rg = lane >> 3;
+    const int col = j0 + warp * 8 + cg;
+    const bool live = col < vdim;
+    const int t0 = seq_start[s], t1 = seq_start[s + 1];
+    if (t1 <= t0) return;
+    float *slot = state + (((size_t)seq_slot[s] * heads + h) * dim) * vdim;
+    const bool fresh = seq_pos0[s] == 0;
+    float S[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int i = rg + 4 * r;
+        S[r] = (!fresh && live && i < dim) ? slot[(size_t)i * vdim + col] : 0.0f;
+    }
+    const float qscale = rsqrtf((float)dim);
+    const int off_k = heads * dim, off_v = 2 * heads * dim;
+    constexpr int EV = TB * kGlaCols / 128;                      // staged values per thread
+    float pa[E], pk[E], pq[E], pv[EV];
+    auto fetch = [&](int tb) {  // global -> registers
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            const int idx = threadIdx.x + e * 128;
+            const int tt = idx / dim, i = idx - tt * dim, t = tb + tt;
+            if (tt < TB && t < t1) {
+                const T *row = proj + (size_t)t * ld;
+                pa[e] = decay[((size_t)t * heads + h) * dim + i];
+                pk[e] = Elem<T>::to_f(row[off_k + h * dim + i]);
+                pq[e] = Elem<T>::to_f(row[h * dim + i]) * qscale;
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < EV; ++e) {
+            const int idx = threadIdx.x + e * 128;
+            const int tt = idx / kGlaCols, c = idx - tt * kGlaCols, t = tb + tt;
+            pv[e] = (t < t1 && j0 + c < vdim) ? Elem<T>::to_f(proj[(size_t)t * ld + off_v + h * vdim + j0 + c]) : 0.0f;
+        }
+    };
+    auto stash = [&](int tb) {  // registers -> shared
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            const int idx = threadIdx.x + e * 128;
+            const int tt = idx / dim, i = idx - tt * dim;
+            if (tt < TB && tb + tt < t1) akq[tt * dim + i] = make_float4(pa[e], pk[e], pq[e], 0.0f);
+        }
+#pragma unroll
+        for (int e = 0; e < EV; ++e) vs[threadIdx.x + e * 128] = pv[e];
+    };
+    fetch(t0);
+    for (int tb = t0; tb < t1; tb += TB) {
+        __syncthreads();  // the previous block has been consumed
+        stash(tb);
+        __syncthreads();
+        if (tb + TB < t1) fetch(tb + TB);
+        const int nt = min(TB, t1 - tb);
+        for (int tt = 0; tt < nt; ++tt) {
+            const float v = vs[tt * kGlaCols + warp * 8 + cg];
+            const float4 *row = akq + tt * dim + rg;
+            float acc = 0.0f;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                if (rg + 4 * r < dim) {
+                    const float4 x = row[4 * r];
+                    S[r] = fmaf(x.x, S[r], x.y * v);
+                    acc = fmaf(S[r], x.z, acc);
+                }
+            }
+            acc += __shfl_xor_sync(0xffffffffu, acc, 8);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 16);
+            if (rg == 0 && live) o[((size_t)(tb + tt) * heads + h) * vdim + col] = acc;
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int i = rg + 4 * r;
+            if (i < dim) slot[(size_t)i * vdim + col] = S[r];
+        }
+    }
+}
+
+template <typename T, int R, int TB>
+static void launch_gla_reg(const void *proj, int ld, const float *decay, float *state, float *o, const int *seq_start, const int *seq_pos0,
+                           const int *seq_slot, dim3 grid, int heads, int dim, int vdim, cudaStream_t st) {
+    const size_t smem = ((size_t)TB * dim * 4 + (size_t)TB * kGlaCols) * sizeof(float);
+    if (smem > 48 * 1024) cudaFuncSetAttribute(gla_recurrent_reg_kernel<T, R, TB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    gla_recurrent_reg_kernel<T, R, TB><<<grid, 128, smem, st>>>((const T *)proj, ld, decay, state, o, seq_start, seq_pos0, seq_slot, heads, dim, vdim);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128)
 gla_output_kernel(const float *__restrict__ o, const float *__restrict__ w, float eps, const T *__restrict__ gate_in, int gate_ld,
@@ -123,6 +224,14 @@ int launch_gla_recurrent(int dtype, const void *proj, int ld, const float *decay
         return B200_ERR_UNSUPPORTED;
     }
     const dim3 grid((vdim + kGlaCols - 1) / kGlaCols, heads, n_seqs);
+    if (dim <= 256) {
+        B200_DISPATCH_DTYPE(dtype, {
+            if (dim <= 64) launch_gla_reg<T, 16, 16>(proj, ld, decay, state, o, seq_start, seq_pos0, seq_slot, grid, heads, dim, vdim, st);
+            else if (dim <= 128) launch_gla_reg<T, 32, 16>(proj, ld, decay, state, o, seq_start, seq_pos0, seq_slot, grid, heads, dim, vdim, st);
+            else launch_gla_reg<T, 64, 8>(proj, ld, decay, state, o, seq_start, seq_pos0, seq_slot, grid, heads, dim, vdim, st);
+        });
+        return cuda_status("gla_recurrent launch");
+    }
     B200_DISPATCH_DTYPE(dtype, {
         if (smem > 48 * 1024) cudaFuncSetAttribute(gla_recurrent_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         gla_recurrent_kernel<T><<<grid, kGlaThreads, smem, st>>>((const T *)proj, ld, decay, state, o, seq_start, seq_pos0, seq_slot, heads, dim,
