@@ -14,21 +14,39 @@ namespace b200 {
 constexpr int kGlaCols = 32;     // columns of S per CTA
 constexpr int kGlaThreads = 256; // 8 row groups x 32 columns
 
+// One CTA per block of kDecayTokens tokens: a thread reads a row of the second decay matrix once and uses it for every token of the block.
+constexpr int kDecayTokens = 16;
 template <typename T>
 __global__ void __launch_bounds__(256)
 gla_decay_kernel(const T *__restrict__ proj, int ld, int col0, const T *__restrict__ w, const float *__restrict__ bias, float inv_tau,
-                 float *__restrict__ decay, int rank, int channels) {
-    extern __shared__ float lo[];  // the token's low-rank vector
-    const int t = blockIdx.x;
-    for (int r = threadIdx.x; r < rank; r += blockDim.x) lo[r] = Elem<T>::to_f(proj[(size_t)t * ld + col0 + r]);
+                 float *__restrict__ decay, int tokens, int rank, int channels) {
+    extern __shared__ float lo[];  // [kDecayTokens][rank]: the tokens' low-rank vectors
+    const int t0 = blockIdx.x * kDecayTokens;
+    const int nt = min(kDecayTokens, tokens - t0);
+    for (int i = threadIdx.x; i < kDecayTokens * rank; i += blockDim.x) {
+        const int tt = i / rank, r = i - tt * rank;
+        lo[i] = tt < nt ? Elem<T>::to_f(proj[(size_t)(t0 + tt) * ld + col0 + r]) : 0.0f;
+    }
     __syncthreads();
     for (int c = threadIdx.x; c < channels; c += blockDim.x) {
-        float z = bias ? bias[c] : 0.0f;
+        float z[kDecayTokens];
+        const float b0 = bias ? bias[c] : 0.0f;
+#pragma unroll
+        for (int tt = 0; tt < kDecayTokens; ++tt) z[tt] = b0;
         const T *wr = w + (size_t)c * rank;
-        for (int r = 0; r < rank; ++r) z = fmaf(Elem<T>::to_f(wr[r]), lo[r], z);
-        // log sigmoid(z) = min(z, 0) - log1p(exp(-|z|));  a = exp(log sigmoid(z) / tau)
-        const float ls = fminf(z, 0.0f) - log1pf(expf(-fabsf(z)));
-        decay[(size_t)t * channels + c] = expf(ls * inv_tau);
+        for (int r = 0; r < rank; ++r) {
+            const float wv = Elem<T>::to_f(wr[r]);
+#pragma unroll
+            for (int tt = 0; tt < kDecayTokens; ++tt) z[tt] = fmaf(wv, lo[tt * rank + r], z[tt]);
+        }
+#pragma unroll
+        for (int tt = 0; tt < kDecayTokens; ++tt) {
+            if (tt < nt) {
+                // log sigmoid(z) = min(z, 0) - log1p(exp(-|z|));  a = exp(log sigmoid(z) / tau)
+                const float ls = fminf(z[tt], 0.0f) - log1pf(expf(-fabsf(z[tt])));
+                decay[(size_t)(t0 + tt) * channels + c] = expf(ls * inv_tau);
+            }
+        }
     }
 }
 
@@ -86,105 +104,143 @@ gla_recurrent_kernel(const T *__restrict__ proj, int ld, const float *__restrict
         for (int i = rg; i < dim; i += kRowGroups) slot[(size_t)i * vdim + j0 + col] = S[i * kGlaCols + col];
 }
 
-// Register-resident variant (dim <= 4 * R): the tile of S lives in registers, R rows per thread.  A warp owns 8 columns; its lanes are
-// 8 columns x 4 row groups (rows rg, rg + 4, ...), so the sum over rows ends with two shuffles and no barrier.  Tokens are staged in
-// blocks of TB: {decay, k, q} of a row as one float4 in shared memory (one 16-byte broadcast load per row and token), the next block's
-// global loads are issued before the current block is computed.  One barrier pair per TB tokens.
-template <typename T, int R, int TB>
-__global__ void __launch_bounds__(128)
+// Register-resident variant (dim <= 32 * RR): the tile of S lives in registers.  A warp owns 8 columns; lane l holds rows l, l + 32, ...
+// (RR of them) of those 8 columns, so {decay, k, q} of a row -- one float4 in shared memory -- is loaded once per token and row and used
+// for 8 columns, and the 32 lanes read 32 different rows (no broadcast, no bank conflict).  The sum over rows is a butterfly that halves
+// the column set at every exchange (4 + 2 + 1 + 1 + 1 shuffles for 8 columns).  Tokens are staged in blocks of TB by four PRODUCER warps
+// (global -> fp32 -> shared, two stages) while the four compute warps work on the block before: the global-load latency, which a single
+// compute warp per scheduler cannot hide, is off the recurrence's path.  Rows >= dim are zero rows in shared memory: no bounds inside.
+constexpr int kGlaWarpCols = 8;
+template <typename T, int RR, int TB>
+__global__ void __launch_bounds__(256)
 gla_recurrent_reg_kernel(const T *__restrict__ proj, int ld, const float *__restrict__ decay, float *__restrict__ state, float *__restrict__ o,
                          const int *__restrict__ seq_start, const int *__restrict__ seq_pos0, const int *__restrict__ seq_slot, int heads,
                          int dim, int vdim) {
     extern __shared__ __align__(16) float smf[];
-    float4 *akq = reinterpret_cast<float4 *>(smf);              // [TB][dim]
-    float *vs = smf + (size_t)TB * dim * 4;                      // [TB][32]
-    constexpr int E = TB * R / 32;                               // staged (row, token) pairs per thread
+    constexpr int DP = 32 * RR;                                  // padded rows
+    constexpr int kStage = TB * DP * 4 + TB * kGlaCols;          // floats per stage: {a, k, q, -} [TB][DP] | v [TB][32]
+    constexpr int E = TB * DP / 128;                             // staged (token, row) pairs per producer thread
+    constexpr int EV = TB * kGlaCols / 128;
     const int j0 = blockIdx.x * kGlaCols, h = blockIdx.y, s = blockIdx.z;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, cg = lane & 7, rg = lane >> 3;
-    const int col = j0 + warp * 8 + cg;
-    const bool live = col < vdim;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool producer = warp >= 4;                             // warps 4..7 stage the next block of tokens while warps 0..3 compute
+    const int c0 = j0 + (warp & 3) * kGlaWarpCols;
     const int t0 = seq_start[s], t1 = seq_start[s + 1];
     if (t1 <= t0) return;
     float *slot = state + (((size_t)seq_slot[s] * heads + h) * dim) * vdim;
     const bool fresh = seq_pos0[s] == 0;
-    float S[R];
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-        const int i = rg + 4 * r;
-        S[r] = (!fresh && live && i < dim) ? slot[(size_t)i * vdim + col] : 0.0f;
-    }
     const float qscale = rsqrtf((float)dim);
     const int off_k = heads * dim, off_v = 2 * heads * dim;
-    constexpr int EV = TB * kGlaCols / 128;                      // staged values per thread
-    float pa[E], pk[E], pq[E], pv[EV];
-    auto fetch = [&](int tb) {  // global -> registers
+    auto fill = [&](int tb, int stage) {  // producer threads: global -> shared, fp32, rows >= dim and tokens >= t1 as zeros
+        float4 *akq = reinterpret_cast<float4 *>(smf + stage * kStage);
+        float *vs = smf + stage * kStage + TB * DP * 4;
+        const int ptid = threadIdx.x - 128;
 #pragma unroll
         for (int e = 0; e < E; ++e) {
-            const int idx = threadIdx.x + e * 128;
-            const int tt = idx / dim, i = idx - tt * dim, t = tb + tt;
-            if (tt < TB && t < t1) {
+            const int idx = ptid + e * 128;
+            const int tt = idx / DP, i = idx % DP, t = tb + tt;
+            float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (t < t1 && i < dim) {
                 const T *row = proj + (size_t)t * ld;
-                pa[e] = decay[((size_t)t * heads + h) * dim + i];
-                pk[e] = Elem<T>::to_f(row[off_k + h * dim + i]);
-                pq[e] = Elem<T>::to_f(row[h * dim + i]) * qscale;
+                x.x = decay[((size_t)t * heads + h) * dim + i];
+                x.y = Elem<T>::to_f(row[off_k + h * dim + i]);
+                x.z = Elem<T>::to_f(row[h * dim + i]) * qscale;
             }
+            akq[idx] = x;
         }
 #pragma unroll
         for (int e = 0; e < EV; ++e) {
-            const int idx = threadIdx.x + e * 128;
-            const int tt = idx / kGlaCols, c = idx - tt * kGlaCols, t = tb + tt;
-            pv[e] = (t < t1 && j0 + c < vdim) ? Elem<T>::to_f(proj[(size_t)t * ld + off_v + h * vdim + j0 + c]) : 0.0f;
+            const int idx = ptid + e * 128;
+            const int tt = idx / kGlaCols, c = idx % kGlaCols, t = tb + tt;
+            vs[idx] = (t < t1 && j0 + c < vdim) ? Elem<T>::to_f(proj[(size_t)t * ld + off_v + h * vdim + j0 + c]) : 0.0f;
         }
     };
-    auto stash = [&](int tb) {  // registers -> shared
+    float S[RR][kGlaWarpCols];
+    if (!producer) {
 #pragma unroll
-        for (int e = 0; e < E; ++e) {
-            const int idx = threadIdx.x + e * 128;
-            const int tt = idx / dim, i = idx - tt * dim;
-            if (tt < TB && tb + tt < t1) akq[tt * dim + i] = make_float4(pa[e], pk[e], pq[e], 0.0f);
-        }
+        for (int r = 0; r < RR; ++r)
 #pragma unroll
-        for (int e = 0; e < EV; ++e) vs[threadIdx.x + e * 128] = pv[e];
-    };
-    fetch(t0);
-    for (int tb = t0; tb < t1; tb += TB) {
-        __syncthreads();  // the previous block has been consumed
-        stash(tb);
-        __syncthreads();
-        if (tb + TB < t1) fetch(tb + TB);
-        const int nt = min(TB, t1 - tb);
-        for (int tt = 0; tt < nt; ++tt) {
-            const float v = vs[tt * kGlaCols + warp * 8 + cg];
-            const float4 *row = akq + tt * dim + rg;
-            float acc = 0.0f;
-#pragma unroll
-            for (int r = 0; r < R; ++r) {
-                if (rg + 4 * r < dim) {
-                    const float4 x = row[4 * r];
-                    S[r] = fmaf(x.x, S[r], x.y * v);
-                    acc = fmaf(S[r], x.z, acc);
-                }
+            for (int c = 0; c < kGlaWarpCols; ++c) {
+                const int i = lane + 32 * r;
+                S[r][c] = (!fresh && i < dim && c0 + c < vdim) ? slot[(size_t)i * vdim + c0 + c] : 0.0f;
             }
-            acc += __shfl_xor_sync(0xffffffffu, acc, 8);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 16);
-            if (rg == 0 && live) o[((size_t)(tb + tt) * heads + h) * vdim + col] = acc;
-        }
+    } else {
+        fill(t0, 0);
     }
-    if (live) {
+    __syncthreads();
+    int stage = 0;
+    for (int tb = t0; tb < t1; tb += TB, stage ^= 1) {
+        if (producer) {
+            if (tb + TB < t1) fill(tb + TB, stage ^ 1);
+        } else {
+            const float4 *akq = reinterpret_cast<const float4 *>(smf + stage * kStage);
+            const float *vs = smf + stage * kStage + TB * DP * 4;
+            const int nt = min(TB, t1 - tb);
+#pragma unroll 2
+            for (int tt = 0; tt < nt; ++tt) {
+                const float4 v0 = *reinterpret_cast<const float4 *>(vs + tt * kGlaCols + warp * kGlaWarpCols);
+                const float4 v1 = *reinterpret_cast<const float4 *>(vs + tt * kGlaCols + warp * kGlaWarpCols + 4);
+                const float v[kGlaWarpCols] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+                float acc[kGlaWarpCols];
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const int i = rg + 4 * r;
-            if (i < dim) slot[(size_t)i * vdim + col] = S[r];
+                for (int c = 0; c < kGlaWarpCols; ++c) acc[c] = 0.0f;
+#pragma unroll
+                for (int r = 0; r < RR; ++r) {
+                    const float4 x = akq[tt * DP + lane + 32 * r];
+#pragma unroll
+                    for (int c = 0; c < kGlaWarpCols; ++c) {
+                        S[r][c] = fmaf(x.x, S[r][c], x.y * v[c]);
+                        acc[c] = fmaf(S[r][c], x.z, acc[c]);
+                    }
+                }
+                // butterfly over the 32 lanes, halving the columns a lane is responsible for: 8 -> 4 -> 2 -> 1, then two plain steps
+                float a4[4], a2[2], a1;
+                {
+                    const bool up = lane & 16;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const float give = up ? acc[c] : acc[c + 4], keep = up ? acc[c + 4] : acc[c];
+                        a4[c] = keep + __shfl_xor_sync(0xffffffffu, give, 16);
+                    }
+                }
+                {
+                    const bool up = lane & 8;
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        const float give = up ? a4[c] : a4[c + 2], keep = up ? a4[c + 2] : a4[c];
+                        a2[c] = keep + __shfl_xor_sync(0xffffffffu, give, 8);
+                    }
+                }
+                {
+                    const bool up = lane & 4;
+                    const float give = up ? a2[0] : a2[1], keep = up ? a2[1] : a2[0];
+                    a1 = keep + __shfl_xor_sync(0xffffffffu, give, 4);
+                }
+                a1 += __shfl_xor_sync(0xffffffffu, a1, 2);
+                a1 += __shfl_xor_sync(0xffffffffu, a1, 1);
+                // lane l now holds column ((l >> 4) & 1) * 4 + ((l >> 3) & 1) * 2 + ((l >> 2) & 1) of the warp's eight
+                const int c = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+                if ((lane & 3) == 0 && c0 + c < vdim) o[((size_t)(tb + tt) * heads + h) * vdim + c0 + c] = a1;
+            }
         }
+        __syncthreads();  // the next stage is filled and this one consumed
     }
+    if (producer) return;
+#pragma unroll
+    for (int r = 0; r < RR; ++r)
+#pragma unroll
+        for (int c = 0; c < kGlaWarpCols; ++c) {
+            const int i = lane + 32 * r;
+            if (i < dim && c0 + c < vdim) slot[(size_t)i * vdim + c0 + c] = S[r][c];
+        }
 }
 
-template <typename T, int R, int TB>
+template <typename T, int RR, int TB>
 static void launch_gla_reg(const void *proj, int ld, const float *decay, float *state, float *o, const int *seq_start, const int *seq_pos0,
                            const int *seq_slot, dim3 grid, int heads, int dim, int vdim, cudaStream_t st) {
-    const size_t smem = ((size_t)TB * dim * 4 + (size_t)TB * kGlaCols) * sizeof(float);
-    if (smem > 48 * 1024) cudaFuncSetAttribute(gla_recurrent_reg_kernel<T, R, TB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    gla_recurrent_reg_kernel<T, R, TB><<<grid, 128, smem, st>>>((const T *)proj, ld, decay, state, o, seq_start, seq_pos0, seq_slot, heads, dim, vdim);
+    const size_t smem = 2 * ((size_t)TB * 32 * RR * 4 + (size_t)TB * kGlaCols) * sizeof(float);
+    if (smem > 48 * 1024) cudaFuncSetAttribute(gla_recurrent_reg_kernel<T, RR, TB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    gla_recurrent_reg_kernel<T, RR, TB><<<grid, 256, smem, st>>>((const T *)proj, ld, decay, state, o, seq_start, seq_pos0, seq_slot, heads, dim, vdim);
 }
 
 template <typename T>
@@ -209,8 +265,8 @@ int launch_gla_decay(int dtype, const void *proj, int ld, int col0, const void *
                      int tokens, int rank, int channels, cudaStream_t st) {
     if (tokens == 0) return B200_OK;
     B200_DISPATCH_DTYPE(dtype, {
-        gla_decay_kernel<T><<<tokens, 256, (size_t)rank * sizeof(float), st>>>((const T *)proj, ld, col0, (const T *)w_decay, bias, 1.0f / tau,
-                                                                                decay, rank, channels);
+        gla_decay_kernel<T><<<(tokens + kDecayTokens - 1) / kDecayTokens, 256, (size_t)kDecayTokens * rank * sizeof(float), st>>>(
+            (const T *)proj, ld, col0, (const T *)w_decay, bias, 1.0f / tau, decay, tokens, rank, channels);
     });
     return cuda_status("gla_decay launch");
 }
@@ -226,9 +282,10 @@ int launch_gla_recurrent(int dtype, const void *proj, int ld, const float *decay
     const dim3 grid((vdim + kGlaCols - 1) / kGlaCols, heads, n_seqs);
     if (dim <= 256) {
         B200_DISPATCH_DTYPE(dtype, {
-            if (dim <= 64) launch_gla_reg<T, 16, 16>(proj, ld, decay, state, o, seq_start, seq_pos0, seq_slot, grid, heads, dim, vdim, st);
-            else if (dim <= 128) launch_gla_reg<T, 32, 16>(proj, ld, decay, state, o, seq_start, seq_pos0, seq_slot, grid, heads, dim, vdim, st);
-            else launch_gla_reg<T, 64, 8>(proj, ld, decay, state, o, seq_start, seq_pos0, seq_slot, grid, heads, dim, vdim, st);
+            if (dim <= 32) launch_gla_reg<T, 1, 16>(proj, ld, decay, state, o, seq_start, seq_pos0, seq_slot, grid, heads, dim, vdim, st);
+            else if (dim <= 64) launch_gla_reg<T, 2, 16>(proj, ld, decay, state, o, seq_start, seq_pos0, seq_slot, grid, heads, dim, vdim, st);
+            else if (dim <= 128) launch_gla_reg<T, 4, 16>(proj, ld, decay, state, o, seq_start, seq_pos0, seq_slot, grid, heads, dim, vdim, st);
+            else launch_gla_reg<T, 8, 8>(proj, ld, decay, state, o, seq_start, seq_pos0, seq_slot, grid, heads, dim, vdim, st);
         });
         return cuda_status("gla_recurrent launch");
     }

@@ -2,11 +2,11 @@
 // feed-forward of some kind (b200_hybrid_layer_t), run over a ragged mixed batch of portions (b200_hybrid_batch_t).
 //
 // One layer = x += rmsnorm(mixer(x)) * g1;  x += rmsnorm(ff(x)) * g2, with x the fp32 residual stream.  Launch sequence per layer:
-//   cast (16-bit engines) -> fused input projection (b200_linear: tcgen05 GEMM / weight-streaming GEMV by token count)
+//   fused input projection (b200_linear: tcgen05 GEMM / weight-streaming GEMV by token count)
 //   attention mixer:  q/k whole-projection norm + pool append -> chunked sink attention (gate fused) -> output projection
 //   gla mixer:        decay (low-rank, fp32) -> recurrence over the state slots -> head norm * silu(gate) -> output projection
 //   post-norm + residual add (fp32)
-//   moe:              cast -> router + shared gate (fp32) -> route -> plan -> gather (weight on the input) -> grouped up (+act) -> grouped down
+//   moe:              router + shared gate (fp32) -> route -> plan -> gather (weight on the input) -> grouped up (+act) -> grouped down
 //                     shared expert: b200_linear up -> act -> b200_linear down
 //                     combine (sum of the token's expert rows + gate * shared) + post-norm + residual add, one kernel
 // and at the end: final norm of the wanted rows -> LM head with fp32 logits.
@@ -22,26 +22,25 @@ constexpr int kPageH = B200_KV_PAGE_SIZE;
 static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
 template <typename T>
-__global__ void embed_f32_kernel(const int *__restrict__ ids, const T *__restrict__ table, float *__restrict__ x, int width, int vocab) {
+__global__ void embed_f32_kernel(const int *__restrict__ ids, const T *__restrict__ table, float *__restrict__ x, T *__restrict__ h, int width,
+                                 int vocab) {
     const int t = blockIdx.x;
     int id = ids[t];
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // the host has refused ids outside the vocabulary
-    for (int c = threadIdx.x; c < width; c += blockDim.x) x[(size_t)t * width + c] = Elem<T>::to_f(table[(size_t)id * width + c]);
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const T v = table[(size_t)id * width + c];
+        x[(size_t)t * width + c] = Elem<T>::to_f(v);
+        if (h) h[(size_t)t * width + c] = v;  // the 16-bit copy the first projection reads
+    }
 }
 
-template <typename T>
-__global__ void cast_rows_kernel(const float *__restrict__ x, T *__restrict__ h, size_t n) {
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) h[i] = Elem<T>::from_f(x[i]);
-}
-
-// x[t, :] += rmsnorm(y[t, :]) * g, where y is either a dense row (y_dense) or the mixture
+// x[t, :] += rmsnorm(y[t, :]) * g (and h_out[t, :] = T(x[t, :]) for the next projection), where y is either a dense row (y_dense) or the mixture
 //   sum_k y_rows[pair_row[t*top + k], :] + shared_gate[t] * y_shared[t, :].   trace (optional) receives the new x.
 template <typename T>
 __global__ void __launch_bounds__(256)
 postnorm_residual_kernel(float *__restrict__ x, const T *__restrict__ y_dense, const T *__restrict__ y_rows, const int *__restrict__ pair_row,
                          int top, const T *__restrict__ y_shared, const float *__restrict__ shared_gate, const float *__restrict__ g, float eps,
-                         int width, float *__restrict__ trace) {
+                         int width, float *__restrict__ trace, T *__restrict__ h_out) {
     extern __shared__ float ys[];  // [width]
     __shared__ float red[33];
     const int t = blockIdx.x;
@@ -64,12 +63,14 @@ postnorm_residual_kernel(float *__restrict__ x, const T *__restrict__ y_dense, c
         const float v = x[(size_t)t * width + c] + ys[c] * inv * g[c];
         x[(size_t)t * width + c] = v;
         if (trace) trace[(size_t)t * width + c] = v;
+        if (h_out) h_out[(size_t)t * width + c] = Elem<T>::from_f(v);  // what the next sublayer's projections read (16-bit engines)
     }
 }
 
+template <typename T>
 __global__ void __launch_bounds__(256)
 final_norm_rows_kernel(const float *__restrict__ x, const int *__restrict__ rows, const float *__restrict__ g, float eps, float *__restrict__ out,
-                       int width) {
+                       T *__restrict__ out_t, int width) {
     __shared__ float red[33];
     const int i = blockIdx.x;
     const float *xr = x + (size_t)rows[i] * width;
@@ -77,43 +78,73 @@ final_norm_rows_kernel(const float *__restrict__ x, const int *__restrict__ rows
     for (int c = threadIdx.x; c < width; c += blockDim.x) ss = fmaf(xr[c], xr[c], ss);
     ss = block_sum(ss, red);
     const float inv = rsqrtf(ss / (float)width + eps);
-    for (int c = threadIdx.x; c < width; c += blockDim.x) out[(size_t)i * width + c] = xr[c] * inv * g[c];
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float v = xr[c] * inv * g[c];
+        out[(size_t)i * width + c] = v;
+        if (out_t) out_t[(size_t)i * width + c] = Elem<T>::from_f(v);
+    }
 }
 
-// y[m, n] = sum_k x[m, k] w[n, k] (+ bias[n]), fp32 out.  One warp per output column n and tile of kPM rows: a weight row is read once
-// per kPM activations.  Used where the result must stay fp32: router logits and the LM head.
-constexpr int kPM = 8;
-template <typename TX, typename TW>
+// y[m, n] = sum_k x[m, k] w[n, k] (+ bias[n]), fp32 out: used where the result must stay fp32 (router logits, the LM head).
+// A CTA stages PM rows of x in shared memory (fp32) and its 8 warps walk the CTA's slice of output columns: a weight row is read once per
+// PM activations and the activations once per CTA.
+template <typename TX, typename TW, int PM>
 __global__ void __launch_bounds__(256)
 proj_f32_kernel(const TX *__restrict__ x, int ldx, const TW *__restrict__ w, const float *__restrict__ bias, float *__restrict__ y, int ldy, int M,
-                int N, int K) {
-    const int n = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * kPM;
-    if (n >= N) return;
-    float acc[kPM] = {};
-    const TW *wr = w + (size_t)n * K;
-    for (int k = lane; k < K; k += 32) {
-        const float wv = Elem<TW>::to_f(wr[k]);
-#pragma unroll
-        for (int i = 0; i < kPM; ++i)
-            if (m0 + i < M) acc[i] = fmaf(Elem<TX>::to_f(x[(size_t)(m0 + i) * ldx + k]), wv, acc[i]);
+                int N, int K, int cols_per_cta) {
+    extern __shared__ float xs[];  // [PM][K]
+    const int m0 = blockIdx.y * PM, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int i = threadIdx.x; i < PM * K; i += blockDim.x) {
+        const int mm = i / K, k = i - mm * K;
+        xs[i] = m0 + mm < M ? Elem<TX>::to_f(x[(size_t)(m0 + mm) * ldx + k]) : 0.0f;
     }
+    __syncthreads();
+    const int n_end = min(N, (int)(blockIdx.x + 1) * cols_per_cta);
+    for (int n = blockIdx.x * cols_per_cta + warp; n < n_end; n += 8) {
+        float acc[PM] = {};
+        const TW *wr = w + (size_t)n * K;
+        for (int k = lane; k < K; k += 32) {
+            const float wv = Elem<TW>::to_f(wr[k]);
 #pragma unroll
-    for (int i = 0; i < kPM; ++i) {
-        const float v = warp_sum(acc[i]);
-        if (lane == 0 && m0 + i < M) y[(size_t)(m0 + i) * ldy + n] = v + (bias ? bias[n] : 0.0f);
+            for (int i = 0; i < PM; ++i) acc[i] = fmaf(xs[i * K + k], wv, acc[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < PM; ++i) {
+            const float v = warp_sum(acc[i]);
+            if (lane == 0 && m0 + i < M) y[(size_t)(m0 + i) * ldy + n] = v + (bias ? bias[n] : 0.0f);
+        }
     }
+}
+
+template <typename TX, typename TW, int PM>
+static void launch_proj_f32_t(const void *x, int ldx, const void *w, const float *bias, float *y, int ldy, int M, int N, int K, cudaStream_t st) {
+    const size_t smem = (size_t)PM * K * sizeof(float);
+    // enough CTAs to fill the device, at least 8 columns (one per warp) each
+    const int mt = (M + PM - 1) / PM;
+    int cols = (N * mt + 4 * 148 - 1) / (4 * 148);
+    cols = cols < 8 ? 8 : (cols + 7) / 8 * 8;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(proj_f32_kernel<TX, TW, PM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    proj_f32_kernel<TX, TW, PM><<<dim3((N + cols - 1) / cols, mt), 256, smem, st>>>((const TX *)x, ldx, (const TW *)w, bias, y, ldy, M, N, K, cols);
 }
 
 int launch_proj_f32(int x_dtype, const void *x, int ldx, int w_dtype, const void *w, const float *bias, float *y, int ldy, int M, int N,
                     int K, cudaStream_t st) {
     if (M == 0) return B200_OK;
-    const dim3 grid((N + 7) / 8, (M + kPM - 1) / kPM);
+    if ((size_t)4 * K * sizeof(float) > 200 * 1024) {
+        set_error("proj_f32: K = %d does not fit the shared-memory activation tile", K);
+        return B200_ERR_UNSUPPORTED;
+    }
+    const bool wide = M > 8 && (size_t)16 * K * sizeof(float) <= 200 * 1024, mid = (size_t)8 * K * sizeof(float) <= 200 * 1024;
     B200_DISPATCH_DTYPE(w_dtype, {
-        if (x_dtype == B200_F32)
-            proj_f32_kernel<float, T><<<grid, 256, 0, st>>>((const float *)x, ldx, (const T *)w, bias, y, ldy, M, N, K);
-        else
-            proj_f32_kernel<T, T><<<grid, 256, 0, st>>>((const T *)x, ldx, (const T *)w, bias, y, ldy, M, N, K);
+        if (x_dtype == B200_F32) {
+            if (wide) launch_proj_f32_t<float, T, 16>(x, ldx, w, bias, y, ldy, M, N, K, st);
+            else if (mid) launch_proj_f32_t<float, T, 8>(x, ldx, w, bias, y, ldy, M, N, K, st);
+            else launch_proj_f32_t<float, T, 4>(x, ldx, w, bias, y, ldy, M, N, K, st);
+        } else {
+            if (wide) launch_proj_f32_t<T, T, 16>(x, ldx, w, bias, y, ldy, M, N, K, st);
+            else if (mid) launch_proj_f32_t<T, T, 8>(x, ldx, w, bias, y, ldy, M, N, K, st);
+            else launch_proj_f32_t<T, T, 4>(x, ldx, w, bias, y, ldy, M, N, K, st);
+        }
     });
     return cuda_status("proj_f32 launch");
 }
@@ -401,19 +432,15 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
         rc = (expr);                 \
         if (rc != B200_OK) return rc; \
     } while (0)
-    B200_DISPATCH_DTYPE(dt, { embed_f32_kernel<T><<<NT, 128, 0, st>>>(d_ids, (const T *)m->embedding, m->x, width, c.vocab); });
-    auto cast_x = [&]() -> const void * {
-        if (f32) return m->x;
-        const size_t n = (size_t)NT * width;
-        if (dt == B200_BF16) cast_rows_kernel<__nv_bfloat16><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(m->x, (__nv_bfloat16 *)m->h, n);
-        else cast_rows_kernel<__half><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(m->x, (__half *)m->h, n);
-        return m->h;
-    };
+    // 16-bit engines: every kernel that writes the residual stream also writes its 16-bit copy h, which the next projections read
+    B200_DISPATCH_DTYPE(dt, { embed_f32_kernel<T><<<NT, 128, 0, st>>>(d_ids, (const T *)m->embedding, m->x, f32 ? nullptr : (T *)m->h, width, c.vocab); });
+    auto cast_x = [&]() -> const void * { return f32 ? (const void *)m->x : (const void *)m->h; };
     auto postnorm = [&](const void *y_dense, const void *y_rows, const int *pair_row, int top, const void *y_shared, const float *gate,
                         const float *g, float *trace) -> int {
         B200_DISPATCH_DTYPE(dt, {
             postnorm_residual_kernel<T><<<NT, 256, (size_t)width * sizeof(float), st>>>(m->x, (const T *)y_dense, (const T *)y_rows, pair_row, top,
-                                                                                      (const T *)y_shared, gate, g, c.norm_eps, width, trace);
+                                                                                      (const T *)y_shared, gate, g, c.norm_eps, width, trace,
+                                                                                      f32 ? nullptr : (T *)m->h);
         });
         return cuda_status("postnorm_residual launch");
     };
@@ -461,7 +488,11 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
                 *n_tiles = tile_expert + max_tiles;
             float *sel_weight = m->moe_f, *row_weight = sel_weight + pairs, *shared_gate = row_weight + max_rows;
             const void *h2 = cast_x();
-            RUN(launch_proj_f32(B200_F32, m->x, width, dt, l.w_router, nullptr, m->f32a, l.experts + 1, NT, l.experts + 1, width, st));
+            // router logits + shared gate, fp32: 16-bit engines multiply the 16-bit copy of x on the tensor cores (products of 16-bit values
+            // are exact in fp32 and the sums are fp32), others -- and widths the tensor-core kernel does not take -- the fp32 kernel
+            rc = launch_dense_f32out(dt, h2, l.w_router, m->f32a, NT, l.experts + 1, width, st);
+            if (rc == B200_ERR_UNSUPPORTED) rc = launch_proj_f32(B200_F32, m->x, width, dt, l.w_router, nullptr, m->f32a, l.experts + 1, NT, l.experts + 1, width, st);
+            if (rc != B200_OK) return rc;
             RUN(launch_moe_route_sigmoid(m->f32a, l.experts + 1, sel_expert, sel_weight, shared_gate, NT, l.experts, l.top, st));
             RUN(launch_moe_plan(sel_expert, sel_weight, row_token, row_weight, tile_expert, pair_row, n_tiles, NT, l.experts, l.top, max_rows, st));
             RUN(launch_moe_gather(dt, m->x, row_token, row_weight, m->xg, n_tiles, max_rows, width, st));
@@ -476,8 +507,11 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
         }
     }
     if (W > 0) {
-        final_norm_rows_kernel<<<W, 256, 0, st>>>(m->x, d_want, m->final_norm, c.norm_eps, m->xn, width);
-        RUN(launch_proj_f32(B200_F32, m->xn, width, dt, m->lm_head, nullptr, logits, c.vocab, W, c.vocab, width, st));
+        // the wanted rows only: final norm (fp32 and, for 16-bit engines, a 16-bit copy in h), then the LM head with fp32 logits
+        B200_DISPATCH_DTYPE(dt, { final_norm_rows_kernel<T><<<W, 256, 0, st>>>(m->x, d_want, m->final_norm, c.norm_eps, m->xn, f32 ? nullptr : (T *)m->h, width); });
+        rc = launch_dense_f32out(dt, m->h, m->lm_head, logits, W, c.vocab, width, st);
+        if (rc == B200_ERR_UNSUPPORTED) rc = launch_proj_f32(B200_F32, m->xn, width, dt, m->lm_head, nullptr, logits, c.vocab, W, c.vocab, width, st);
+        if (rc != B200_OK) return rc;
     }
 #undef RUN
     return cuda_status("hybrid_forward");

@@ -41,6 +41,9 @@ int launch_moe_gather(int dtype, const float *x, const int *row_token, const flo
 // c[row, n] = act?(sum_k a[row, k] * w[tile_expert[row / kMoeTileM]][n, k]);  rows >= n_tiles * kMoeTileM are skipped
 int launch_moe_grouped_gemm(int dtype, const void *a, const void *w, void *c, const int *tile_expert, const int *n_tiles, int max_tiles,
                             int N, int K, int act, cudaStream_t st);
+// y fp32 [M, N] = x [M, K] * w[N, K]^T for 16-bit x and w on the tensor cores (fp32 accumulation, fp32 result); B200_ERR_UNSUPPORTED for
+// fp32 engines and K not a multiple of 8 (the caller falls back to launch_proj_f32)
+int launch_dense_f32out(int dtype, const void *x, const void *w, float *y, int M, int N, int K, cudaStream_t st);
 // in place: x = act(x)
 int launch_activation(int dtype, void *x, size_t n, int act, cudaStream_t st);
 

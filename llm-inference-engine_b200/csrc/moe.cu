@@ -165,16 +165,18 @@ __device__ __forceinline__ void moe_ldsm(unsigned &r0, unsigned &r1, unsigned &r
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
 }
 
-template <typename T>
+// The same kernel serves the dense fp32-output projections of a 16-bit engine (router logits, LM head): tile_expert == NULL (one weight),
+// n_tiles == NULL (every tile of the grid is live), rows >= M are zero-filled on load and not stored, TC = float.
+template <typename T, typename TC>
 __global__ void __launch_bounds__(128)
-moe_grouped_gemm_mma_kernel(const T *__restrict__ a, const T *__restrict__ w, T *__restrict__ c, const int *__restrict__ tile_expert,
-                            const int *__restrict__ n_tiles, int N, int K, int act) {
-    if ((int)blockIdx.y >= *n_tiles) return;
+moe_grouped_gemm_mma_kernel(const T *__restrict__ a, const T *__restrict__ w, TC *__restrict__ c, const int *__restrict__ tile_expert,
+                            const int *__restrict__ n_tiles, int M, int N, int K, int act) {
+    if (n_tiles && (int)blockIdx.y >= *n_tiles) return;
     extern __shared__ __align__(16) unsigned char smraw[];
     T *As = reinterpret_cast<T *>(smraw);               // [stages][64][64]
     T *Bs = As + kMStages * kMoeTileM * kMK;            // [stages][128][64]
     const int m0 = blockIdx.y * kMoeTileM, n0 = blockIdx.x * kMN;
-    const T *wb = w + (size_t)tile_expert[blockIdx.y] * N * K;
+    const T *wb = w + (tile_expert ? (size_t)tile_expert[blockIdx.y] * N * K : 0);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
     const int wm = warp >> 1, wn = warp & 1;
     const int nk = (K + kMK - 1) / kMK;
@@ -183,8 +185,8 @@ moe_grouped_gemm_mma_kernel(const T *__restrict__ a, const T *__restrict__ w, T 
         T *as = As + stage * kMoeTileM * kMK, *bs = Bs + stage * kMN * kMK;
         for (int i = threadIdx.x; i < kMoeTileM * 8; i += 128) {
             const int r = i >> 3, cc = (i & 7) * 8;
-            const bool live = k0 + cc < K;
-            moe_cp16(as + moe_swz(r, cc), a + (size_t)(m0 + r) * K + (live ? k0 + cc : 0), live);
+            const bool live = k0 + cc < K && m0 + r < M;
+            moe_cp16(as + moe_swz(r, cc), a + (live ? (size_t)(m0 + r) * K + k0 + cc : 0), live);
         }
         for (int i = threadIdx.x; i < kMN * 8; i += 128) {
             const int r = i >> 3, cc = (i & 7) * 8;
@@ -232,8 +234,24 @@ moe_grouped_gemm_mma_kernel(const T *__restrict__ a, const T *__restrict__ w, T 
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int m = m0 + wm * 32 + i * 16 + gid + (e >> 1) * 8, n = n0 + wn * 64 + j * 8 + tig * 2 + (e & 1);
-                if (n < N) c[(size_t)m * N + n] = Elem<T>::from_f(act >= 0 ? act_apply(acc[i][j][e], act) : acc[i][j][e]);
+                if (n < N && m < M) c[(size_t)m * N + n] = Elem<TC>::from_f(act >= 0 ? act_apply(acc[i][j][e], act) : acc[i][j][e]);
             }
+}
+
+// y fp32 [M, N] = x [M, K] (16-bit) * w[N, K]^T on the tensor cores, fp32 accumulation and fp32 result
+int launch_dense_f32out(int dtype, const void *x, const void *w, float *y, int M, int N, int K, cudaStream_t st) {
+    if (M == 0) return B200_OK;
+    if (dtype == B200_F32 || K % 8 != 0) return B200_ERR_UNSUPPORTED;
+    const dim3 grid((N + kMN - 1) / kMN, (M + kMoeTileM - 1) / kMoeTileM);
+    const size_t smem = (size_t)kMStages * (kMoeTileM + kMN) * kMK * 2;
+    if (dtype == B200_BF16) {
+        cudaFuncSetAttribute(moe_grouped_gemm_mma_kernel<__nv_bfloat16, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        moe_grouped_gemm_mma_kernel<__nv_bfloat16, float><<<grid, 128, smem, st>>>((const __nv_bfloat16 *)x, (const __nv_bfloat16 *)w, y, nullptr, nullptr, M, N, K, -1);
+    } else {
+        cudaFuncSetAttribute(moe_grouped_gemm_mma_kernel<__half, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        moe_grouped_gemm_mma_kernel<__half, float><<<grid, 128, smem, st>>>((const __half *)x, (const __half *)w, y, nullptr, nullptr, M, N, K, -1);
+    }
+    return cuda_status("dense_f32out launch");
 }
 
 template <typename T>
@@ -271,12 +289,13 @@ int launch_moe_grouped_gemm(int dtype, const void *a, const void *w, void *c, co
         const dim3 grid((N + kMN - 1) / kMN, max_tiles);
         const size_t smem = (size_t)kMStages * (kMoeTileM + kMN) * kMK * 2;
         if (dtype == B200_BF16) {
-            cudaFuncSetAttribute(moe_grouped_gemm_mma_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            moe_grouped_gemm_mma_kernel<__nv_bfloat16><<<grid, 128, smem, st>>>((const __nv_bfloat16 *)a, (const __nv_bfloat16 *)w, (__nv_bfloat16 *)c,
-                                                                                tile_expert, n_tiles, N, K, act);
+            cudaFuncSetAttribute(moe_grouped_gemm_mma_kernel<__nv_bfloat16, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            moe_grouped_gemm_mma_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 128, smem, st>>>((const __nv_bfloat16 *)a, (const __nv_bfloat16 *)w, (__nv_bfloat16 *)c,
+                                                                                               tile_expert, n_tiles, max_tiles * kMoeTileM, N, K, act);
         } else {
-            cudaFuncSetAttribute(moe_grouped_gemm_mma_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            moe_grouped_gemm_mma_kernel<__half><<<grid, 128, smem, st>>>((const __half *)a, (const __half *)w, (__half *)c, tile_expert, n_tiles, N, K, act);
+            cudaFuncSetAttribute(moe_grouped_gemm_mma_kernel<__half, __half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            moe_grouped_gemm_mma_kernel<__half, __half><<<grid, 128, smem, st>>>((const __half *)a, (const __half *)w, (__half *)c, tile_expert, n_tiles,
+                                                                                 max_tiles * kMoeTileM, N, K, act);
         }
         return cuda_status("moe_grouped_gemm (tensor core) launch");
     }
