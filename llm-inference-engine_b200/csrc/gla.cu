@@ -135,24 +135,33 @@ gla_recurrent_reg_kernel(const T *__restrict__ proj, int ld, const float *__rest
         float4 *akq = reinterpret_cast<float4 *>(smf + stage * kStage);
         float *vs = smf + stage * kStage + TB * DP * 4;
         const int ptid = threadIdx.x - 128;
+        // every load first (addresses clamped into range so that none is conditional and all are in flight together), then the stores
+        float ra[E], rk[E], rq[E], rv[EV];
 #pragma unroll
         for (int e = 0; e < E; ++e) {
             const int idx = ptid + e * 128;
-            const int tt = idx / DP, i = idx % DP, t = tb + tt;
-            float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            if (t < t1 && i < dim) {
-                const T *row = proj + (size_t)t * ld;
-                x.x = decay[((size_t)t * heads + h) * dim + i];
-                x.y = Elem<T>::to_f(row[off_k + h * dim + i]);
-                x.z = Elem<T>::to_f(row[h * dim + i]) * qscale;
-            }
-            akq[idx] = x;
+            const int tt = idx / DP, i = min(idx % DP, dim - 1), t = min(tb + tt, t1 - 1);
+            const T *row = proj + (size_t)t * ld;
+            ra[e] = decay[((size_t)t * heads + h) * dim + i];
+            rk[e] = Elem<T>::to_f(row[off_k + h * dim + i]);
+            rq[e] = Elem<T>::to_f(row[h * dim + i]);
         }
 #pragma unroll
         for (int e = 0; e < EV; ++e) {
             const int idx = ptid + e * 128;
-            const int tt = idx / kGlaCols, c = idx % kGlaCols, t = tb + tt;
-            vs[idx] = (t < t1 && j0 + c < vdim) ? Elem<T>::to_f(proj[(size_t)t * ld + off_v + h * vdim + j0 + c]) : 0.0f;
+            const int tt = idx / kGlaCols, c = min(j0 + idx % kGlaCols, vdim - 1), t = min(tb + tt, t1 - 1);
+            rv[e] = Elem<T>::to_f(proj[(size_t)t * ld + off_v + h * vdim + c]);
+        }
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            const int idx = ptid + e * 128;
+            const bool live = tb + idx / DP < t1 && idx % DP < dim;
+            akq[idx] = live ? make_float4(ra[e], rk[e], rq[e] * qscale, 0.0f) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+#pragma unroll
+        for (int e = 0; e < EV; ++e) {
+            const int idx = ptid + e * 128;
+            vs[idx] = (tb + idx / kGlaCols < t1 && j0 + idx % kGlaCols < vdim) ? rv[e] : 0.0f;
         }
     };
     float S[RR][kGlaWarpCols];
@@ -176,12 +185,11 @@ gla_recurrent_reg_kernel(const T *__restrict__ proj, int ld, const float *__rest
             const float4 *akq = reinterpret_cast<const float4 *>(smf + stage * kStage);
             const float *vs = smf + stage * kStage + TB * DP * 4;
             const int nt = min(TB, t1 - tb);
-#pragma unroll 2
-            for (int tt = 0; tt < nt; ++tt) {
+            // one token's update of S and its 8 per-lane partial outputs
+            auto advance = [&](int tt, float *acc) {
                 const float4 v0 = *reinterpret_cast<const float4 *>(vs + tt * kGlaCols + warp * kGlaWarpCols);
                 const float4 v1 = *reinterpret_cast<const float4 *>(vs + tt * kGlaCols + warp * kGlaWarpCols + 4);
                 const float v[kGlaWarpCols] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-                float acc[kGlaWarpCols];
 #pragma unroll
                 for (int c = 0; c < kGlaWarpCols; ++c) acc[c] = 0.0f;
 #pragma unroll
@@ -193,7 +201,9 @@ gla_recurrent_reg_kernel(const T *__restrict__ proj, int ld, const float *__rest
                         acc[c] = fmaf(S[r][c], x.z, acc[c]);
                     }
                 }
-                // butterfly over the 32 lanes, halving the columns a lane is responsible for: 8 -> 4 -> 2 -> 1, then two plain steps
+            };
+            // butterfly over the 32 lanes, halving the columns a lane is responsible for: 8 -> 4 -> 2 -> 1, then two plain steps
+            auto reduce_store = [&](const float *acc, int t) {
                 float a4[4], a2[2], a1;
                 {
                     const bool up = lane & 16;
@@ -220,8 +230,20 @@ gla_recurrent_reg_kernel(const T *__restrict__ proj, int ld, const float *__rest
                 a1 += __shfl_xor_sync(0xffffffffu, a1, 1);
                 // lane l now holds column ((l >> 4) & 1) * 4 + ((l >> 3) & 1) * 2 + ((l >> 2) & 1) of the warp's eight
                 const int c = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
-                if ((lane & 3) == 0 && c0 + c < vdim) o[((size_t)(tb + tt) * heads + h) * vdim + c0 + c] = a1;
+                if ((lane & 3) == 0 && c0 + c < vdim) o[((size_t)t * heads + h) * vdim + c0 + c] = a1;
+            };
+            // the reduction of token t - 1 sits in the same straight-line code as the multiply-adds of token t: its shuffle latency is
+            // covered by them
+            float pacc[kGlaWarpCols], acc[kGlaWarpCols];
+            advance(0, pacc);
+#pragma unroll 2
+            for (int tt = 1; tt < nt; ++tt) {
+                advance(tt, acc);
+                reduce_store(pacc, tb + tt - 1);
+#pragma unroll
+                for (int c = 0; c < kGlaWarpCols; ++c) pacc[c] = acc[c];
             }
+            reduce_store(pacc, tb + nt - 1);
         }
         __syncthreads();  // the next stage is filled and this one consumed
     }
