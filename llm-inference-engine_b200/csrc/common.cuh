@@ -340,6 +340,17 @@ __device__ __forceinline__ void tp_reduce_vec(const TpExchange &t, unsigned int 
     for (int j = 0; j < V; ++j) f[j] = poisoned ? __int_as_float(0x7fc00000) : f[j];
 }
 
+// ------------------------------------------------------------------ activations (b200_act_t)
+__device__ __forceinline__ float act_apply(float v, int act) {
+    if (act == B200_ACT_RELU2) {
+        const float r = fmaxf(v, 0.0f);
+        return r * r;
+    }
+    if (act == B200_ACT_SILU) return v / (1.0f + expf(-v));
+    const float c = 0.7978845608028654f;  // sqrt(2/pi)
+    return 0.5f * v * (1.0f + tanhf(c * (v + 0.044715f * v * v * v)));
+}
+
 // ------------------------------------------------------------------ reductions
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

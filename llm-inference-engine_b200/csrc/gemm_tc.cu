@@ -49,6 +49,12 @@ struct GemmTcParams {
     // B stage), the epilogue reads both halves of the accumulator and writes silu(gate) * up: C [rowsA, I], rowsB = I.  0: plain GEMM.
     int swiglu_inter;
     int swiglu_hw;  // gate (and up) columns per tile: bn = 2 * swiglu_hw (128, 112 or 96: whichever wastes least of the last wave)
+    // Grouped GEMM (mixture of experts): every 128-row tile of A belongs to ONE expert, tile_expert[ta]; B = the experts' weights stacked
+    // [experts * rowsB, K], so tile (ta, tb) multiplies B rows [tile_expert[ta] * rowsB + tb * bn, +bn).  Only the first *n_live row
+    // tiles hold rows (a device-side count: the host launches the worst case); all three roles skip the others alike.  NULL: plain.
+    const int *tile_expert;
+    const int *n_live;
+    int act;        // b200_act_t applied to the result before it is stored, -1: none (plain and grouped GEMM, not the SwiGLU epilogue)
 };
 
 // One contiguous piece of work of a CTA: k-blocks [kb0, kb1) of one output tile.  nslots > 1: the tile is shared with
@@ -235,6 +241,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             int it = 0;
             while (si.next(sg)) {
                 const int ta = sg.tile % p.tilesA, tb = sg.tile / p.tilesA;
+                if (p.tile_expert && ta >= *p.n_live) continue;
+                const int brow = (p.tile_expert ? p.tile_expert[ta] * p.rowsB : 0) + tb * p.bn;
                 for (int kb = sg.kb0; kb < sg.kb1; ++kb, ++it) {
                     const int s = it % p.stages;
                     bar_wait(empty0 + 8 * s, ((it / p.stages) & 1) ^ 1);
@@ -245,7 +253,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         tma_load_2d(sa + kATileBytes, &tmB, kb * kBK, tb * p.swiglu_hw, full0 + 8 * s);
                         tma_load_2d(sa + kATileBytes + p.swiglu_hw * kBK * 2, &tmB, kb * kBK, p.swiglu_inter + tb * p.swiglu_hw, full0 + 8 * s);
                     } else {
-                        tma_load_2d(sa + kATileBytes, &tmB, kb * kBK, tb * p.bn, full0 + 8 * s);
+                        tma_load_2d(sa + kATileBytes, &tmB, kb * kBK, brow, full0 + 8 * s);
                     }
                 }
             }
@@ -257,6 +265,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         Seg sg;
         int it = 0, t = 0;
         for (; si.next(sg); ++t) {
+            if (p.tile_expert && sg.tile % p.tilesA >= *p.n_live) {
+                --t;  // a row tile without rows: not a tile at all for the accumulator rotation
+                continue;
+            }
             const int acc = t % p.acc_bufs;
             bar_wait(tempty0 + 8 * acc, ((t / p.acc_bufs) & 1) ^ 1);  // the epilogue has drained this accumulator
             tc_fence_after();
@@ -289,6 +301,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         int t = 0;
         for (; si.next(sg); ++t) {
             const int ta = sg.tile % p.tilesA, tb = sg.tile / p.tilesA;
+            if (p.tile_expert && ta >= *p.n_live) {
+                --t;
+                continue;
+            }
             const int acc = t % p.acc_bufs;
             bar_wait(tfull0 + 8 * acc, (t / p.acc_bufs) & 1);
             tc_fence_after();
@@ -322,6 +338,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     uint32_t r[16];
                     tc_ld16(taddr + c, r);
                     tc_wait_ld();
+                    if (p.act >= 0) {
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) r[e] = __float_as_uint(act_apply(__uint_as_float(r[e]), p.act));
+                    }
                     if (i < p.rowsA) {
                         if (!p.swap) {
                             const int valid = min(16, p.rowsB - (j0 + c));
@@ -464,6 +484,7 @@ static int launch_gemm_tc_impl(const void *x, const void *w, void *y, int M, int
     GemmTcParams p = {};
     p.C = y, p.ldc = N, p.K = K, p.swap = swap ? 1 : 0, p.is_bf16 = bf16 ? 1 : 0;
     p.swiglu_inter = swiglu_inter;
+    p.act = -1;
     p.kb_total = (K + kBK - 1) / kBK;
     const void *a_ptr, *b_ptr;
     int rows_b_map;  // rows of the B tensor as the TMA sees it
@@ -555,6 +576,46 @@ int launch_gemm_tc(const void *x, const void *w, void *y, int M, int N, int K, i
 // kernel (prefill sizes, M > 128); the [M, 2 * inter] intermediate is never written.  B200_ERR_UNSUPPORTED: use the two launchers.
 int launch_gemm_tc_swiglu(const void *x, const void *w, void *act, int M, int inter, int K, int dtype, cudaStream_t st) {
     return launch_gemm_tc_impl(x, w, act, M, inter, K, dtype, inter, st);
+}
+
+// c[row, :] = act?(a[row, :] . W_e^T) with e = tile_expert[row / 128]: the experts' up or down projection as ONE launch.  a [max_rows, K]
+// (rows grouped by expert, every expert padded to whole 128-row tiles), w [experts * N, K], c [max_rows, N]; *n_live row tiles are live.
+int launch_gemm_tc_grouped(const void *a, const void *w, void *c, int max_rows, int N, int K, int experts, const int *tile_expert,
+                           const int *n_live, int act, int dtype, cudaStream_t st) {
+    if (dtype != B200_BF16 && dtype != B200_F16) return B200_ERR_UNSUPPORTED;
+    if (max_rows < kBM || max_rows % kBM != 0 || K % 8 != 0 || K < kBK || N < 16 || !aligned16(a) || !aligned16(w) || !c) return B200_ERR_UNSUPPORTED;
+    const bool bf16 = dtype == B200_BF16;
+    GemmTcParams p = {};
+    p.C = c, p.ldc = N, p.K = K, p.swap = 0, p.is_bf16 = bf16 ? 1 : 0;
+    p.act = act, p.tile_expert = tile_expert, p.n_live = n_live;
+    p.kb_total = (K + kBK - 1) / kBK;
+    p.rowsA = max_rows, p.rowsB = N;
+    p.bn = N >= 256 ? 256 : (N + 15) / 16 * 16;
+    p.tilesA = max_rows / kBM;
+    p.tiles = p.tilesA * ((N + p.bn - 1) / p.bn);
+    const int sms = sm_count();
+    const int grid = p.tiles < sms ? p.tiles : sms;
+    p.acc_bufs = 2 * p.bn <= 512 ? 2 : 1;
+    p.acc_stride = p.bn > 128 ? 256 : p.bn;
+    p.tmem_cols = pow2_cols(p.acc_bufs == 2 ? p.acc_stride + p.bn : p.bn);
+    const int stage_bytes = kATileBytes + p.bn * kBK * 2;
+    int stages = (int)((200 * 1024) / stage_bytes);
+    if (stages > kMaxStages) stages = kMaxStages;
+    if (stages < 2) return B200_ERR_UNSUPPORTED;
+    p.stages = stages;
+    const size_t smem = (size_t)stages * stage_bytes + 1024 + (2 * kMaxStages + 4) * 8 + 16;
+    CUtensorMap tmA, tmB;
+    if (!make_map(&tmA, a, max_rows, K, kBM, bf16) || !make_map(&tmB, w, experts * N, K, p.bn, bf16)) {
+        set_error("gemm_tc grouped: cuTensorMapEncodeTiled failed (rows %d, experts %d x %d, K %d)", max_rows, experts, N, K);
+        return B200_ERR_CUDA;
+    }
+    auto launch = [&](auto kern) {
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        launch_pdl(kern, dim3(grid), dim3(kTcThreads), smem, st, true, tmA, tmB, p);
+    };
+    if (bf16) launch(gemm_tc_kernel<__nv_bfloat16>);
+    else launch(gemm_tc_kernel<__half>);
+    return cuda_status("gemm_tc grouped launch");
 }
 
 }  // namespace b200

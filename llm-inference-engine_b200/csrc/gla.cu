@@ -28,7 +28,7 @@ gla_decay_kernel(const T *__restrict__ proj, int ld, int col0, const T *__restri
         lo[i] = tt < nt ? Elem<T>::to_f(proj[(size_t)(t0 + tt) * ld + col0 + r]) : 0.0f;
     }
     __syncthreads();
-    for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
         float z[kDecayTokens];
         const float b0 = bias ? bias[c] : 0.0f;
 #pragma unroll
@@ -287,7 +287,10 @@ int launch_gla_decay(int dtype, const void *proj, int ld, int col0, const void *
                      int tokens, int rank, int channels, cudaStream_t st) {
     if (tokens == 0) return B200_OK;
     B200_DISPATCH_DTYPE(dtype, {
-        gla_decay_kernel<T><<<(tokens + kDecayTokens - 1) / kDecayTokens, 256, (size_t)kDecayTokens * rank * sizeof(float), st>>>(
+        // few token blocks (decoding): the channels are spread over CTAs as well
+        const int nb = (tokens + kDecayTokens - 1) / kDecayTokens;
+        const int cb = nb >= 64 ? 1 : (channels + 255) / 256;
+        gla_decay_kernel<T><<<dim3(nb, cb), 256, (size_t)kDecayTokens * rank * sizeof(float), st>>>(
             (const T *)proj, ld, col0, (const T *)w_decay, bias, 1.0f / tau, decay, tokens, rank, channels);
     });
     return cuda_status("gla_decay launch");

@@ -116,6 +116,29 @@ proj_f32_kernel(const TX *__restrict__ x, int ldx, const TW *__restrict__ w, con
     }
 }
 
+// Few outputs (a decode batch's router logits): one warp per output element, four independent partial sums per lane.
+template <typename TX, typename TW>
+__global__ void __launch_bounds__(256)
+proj_f32_small_kernel(const TX *__restrict__ x, int ldx, const TW *__restrict__ w, const float *__restrict__ bias, float *__restrict__ y, int ldy,
+                      int M, int N, int K) {
+    const int o = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (o >= M * N) return;
+    const int mrow = o / N, n = o - mrow * N;
+    const TX *xr = x + (size_t)mrow * ldx;
+    const TW *wr = w + (size_t)n * K;
+    float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+    int k = lane;
+    for (; k + 96 < K; k += 128) {
+        a0 = fmaf(Elem<TX>::to_f(xr[k]), Elem<TW>::to_f(wr[k]), a0);
+        a1 = fmaf(Elem<TX>::to_f(xr[k + 32]), Elem<TW>::to_f(wr[k + 32]), a1);
+        a2 = fmaf(Elem<TX>::to_f(xr[k + 64]), Elem<TW>::to_f(wr[k + 64]), a2);
+        a3 = fmaf(Elem<TX>::to_f(xr[k + 96]), Elem<TW>::to_f(wr[k + 96]), a3);
+    }
+    for (; k < K; k += 32) a0 = fmaf(Elem<TX>::to_f(xr[k]), Elem<TW>::to_f(wr[k]), a0);
+    const float v = warp_sum((a0 + a1) + (a2 + a3));
+    if (lane == 0) y[(size_t)mrow * ldy + n] = v + (bias ? bias[n] : 0.0f);
+}
+
 template <typename TX, typename TW, int PM>
 static void launch_proj_f32_t(const void *x, int ldx, const void *w, const float *bias, float *y, int ldy, int M, int N, int K, cudaStream_t st) {
     const size_t smem = (size_t)PM * K * sizeof(float);
@@ -130,6 +153,14 @@ static void launch_proj_f32_t(const void *x, int ldx, const void *w, const float
 int launch_proj_f32(int x_dtype, const void *x, int ldx, int w_dtype, const void *w, const float *bias, float *y, int ldy, int M, int N,
                     int K, cudaStream_t st) {
     if (M == 0) return B200_OK;
+    if ((long long)M * N <= 8192) {
+        const int grid = (M * N + 7) / 8;
+        B200_DISPATCH_DTYPE(w_dtype, {
+            if (x_dtype == B200_F32) proj_f32_small_kernel<float, T><<<grid, 256, 0, st>>>((const float *)x, ldx, (const T *)w, bias, y, ldy, M, N, K);
+            else proj_f32_small_kernel<T, T><<<grid, 256, 0, st>>>((const T *)x, ldx, (const T *)w, bias, y, ldy, M, N, K);
+        });
+        return cuda_status("proj_f32 (small) launch");
+    }
     if ((size_t)4 * K * sizeof(float) > 200 * 1024) {
         set_error("proj_f32: K = %d does not fit the shared-memory activation tile", K);
         return B200_ERR_UNSUPPORTED;
@@ -186,7 +217,7 @@ struct Carve {
 
 int max_rows_of(const b200_hybrid_config_t &c, const b200_hybrid_layer_t &l) {
     const int pairs = c.max_tokens * l.top;
-    return ((pairs + kMoeTileM - 1) / kMoeTileM + l.experts) * kMoeTileM;
+    return ((pairs + 127) / 128 + l.experts) * 128;  // the larger of the two row-tile sizes
 }
 
 int n_in_of(const b200_hybrid_layer_t &l) {
@@ -482,22 +513,31 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
         if (l.mlp == B200_MLP_MOE) {
             trace = layer_trace ? layer_trace + (size_t)li * NT * width : nullptr;
             const int pairs = NT * l.top;
-            const int max_rows = ((pairs + kMoeTileM - 1) / kMoeTileM + std::min(l.experts, pairs)) * kMoeTileM;
-            const int max_tiles = max_rows / kMoeTileM;
+            // prompt-sized batches of a 16-bit engine: 128-row tiles on the tcgen05 grouped GEMM; otherwise 64-row tiles on mma.sync / SIMT
+            const bool tc = !f32 && pairs >= 1024 && width % 8 == 0 && l.expert_ff % 8 == 0 && width >= 64 && l.expert_ff >= 64;
+            const int tile = tc ? 128 : kMoeTileM;
+            const int max_rows = ((pairs + tile - 1) / tile + std::min(l.experts, pairs)) * tile;
+            const int max_tiles = max_rows / tile;
             int *sel_expert = m->moe_i, *pair_row = sel_expert + pairs, *row_token = pair_row + pairs, *tile_expert = row_token + max_rows,
                 *n_tiles = tile_expert + max_tiles;
             float *sel_weight = m->moe_f, *row_weight = sel_weight + pairs, *shared_gate = row_weight + max_rows;
             const void *h2 = cast_x();
             // router logits + shared gate, fp32: 16-bit engines multiply the 16-bit copy of x on the tensor cores (products of 16-bit values
             // are exact in fp32 and the sums are fp32), others -- and widths the tensor-core kernel does not take -- the fp32 kernel
-            rc = launch_dense_f32out(dt, h2, l.w_router, m->f32a, NT, l.experts + 1, width, st);
+            // (a decode batch is a single 64-row tile there -- one CTA walking all of K -- so few tokens take the fp32 kernel as well)
+            rc = NT >= 64 ? launch_dense_f32out(dt, h2, l.w_router, m->f32a, NT, l.experts + 1, width, st) : B200_ERR_UNSUPPORTED;
             if (rc == B200_ERR_UNSUPPORTED) rc = launch_proj_f32(B200_F32, m->x, width, dt, l.w_router, nullptr, m->f32a, l.experts + 1, NT, l.experts + 1, width, st);
             if (rc != B200_OK) return rc;
             RUN(launch_moe_route_sigmoid(m->f32a, l.experts + 1, sel_expert, sel_weight, shared_gate, NT, l.experts, l.top, st));
-            RUN(launch_moe_plan(sel_expert, sel_weight, row_token, row_weight, tile_expert, pair_row, n_tiles, NT, l.experts, l.top, max_rows, st));
-            RUN(launch_moe_gather(dt, m->x, row_token, row_weight, m->xg, n_tiles, max_rows, width, st));
-            RUN(launch_moe_grouped_gemm(dt, m->xg, l.w_up, m->u, tile_expert, n_tiles, max_tiles, l.expert_ff, width, l.act, st));
-            RUN(launch_moe_grouped_gemm(dt, m->u, l.w_down, m->yrows, tile_expert, n_tiles, max_tiles, width, l.expert_ff, -1, st));
+            RUN(launch_moe_plan(sel_expert, sel_weight, row_token, row_weight, tile_expert, pair_row, n_tiles, NT, l.experts, l.top, tile, st));
+            RUN(launch_moe_gather(dt, m->x, row_token, row_weight, m->xg, n_tiles, max_rows, width, tile, st));
+            if (tc) {
+                RUN(launch_gemm_tc_grouped(m->xg, l.w_up, m->u, max_rows, l.expert_ff, width, l.experts, tile_expert, n_tiles, l.act, dt, st));
+                RUN(launch_gemm_tc_grouped(m->u, l.w_down, m->yrows, max_rows, width, l.expert_ff, l.experts, tile_expert, n_tiles, -1, dt, st));
+            } else {
+                RUN(launch_moe_grouped_gemm(dt, m->xg, l.w_up, m->u, tile_expert, n_tiles, max_tiles, l.expert_ff, width, l.act, st));
+                RUN(launch_moe_grouped_gemm(dt, m->u, l.w_down, m->yrows, tile_expert, n_tiles, max_tiles, width, l.expert_ff, -1, st));
+            }
             if (l.shared_ff > 0) {
                 RUN(linear(m, h2, l.w_shared_up, m->us, NT, width, l.shared_ff, st));
                 RUN(launch_activation(dt, m->us, (size_t)NT * l.shared_ff, l.act, st));

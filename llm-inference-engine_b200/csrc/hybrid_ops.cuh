@@ -30,14 +30,17 @@ int launch_gla_output(int dtype, const float *o, const float *w, float eps, cons
 // moe.cu
 int launch_moe_route_sigmoid(const float *logits, int ld, int *sel_expert, float *sel_weight, float *shared_gate, int tokens,
                              int experts, int top, cudaStream_t st);
-constexpr int kMoeTileM = 64;  // rows of one expert are padded to whole tiles of this many
+constexpr int kMoeTileM = 64;  // rows of one expert are padded to whole tiles of this many (128 when the tcgen05 grouped GEMM runs)
 // Groups the (token, choice) pairs by expert.  row_token / row_weight [max_rows]: token of every padded row (-1: padding) and its routing
 // weight; tile_expert [max_tiles]; pair_row [tokens*top]: the row each pair landed in; n_tiles: device int.
 int launch_moe_plan(const int *sel_expert, const float *sel_weight, int *row_token, float *row_weight, int *tile_expert, int *pair_row,
-                    int *n_tiles, int tokens, int experts, int top, int max_rows, cudaStream_t st);
+                    int *n_tiles, int tokens, int experts, int top, int tile, cudaStream_t st);
 // xg[row, :] = T(weight[row] * x[token[row], :]) (zeros for padding rows): the routing weight multiplies the expert's INPUT
 int launch_moe_gather(int dtype, const float *x, const int *row_token, const float *row_weight, void *xg, const int *n_tiles,
-                      int max_rows, int width, cudaStream_t st);
+                      int max_rows, int width, int tile, cudaStream_t st);
+// gemm_tc.cu: the same product on tcgen05 for row tiles of 128 (16-bit dtypes, K >= 64 and a multiple of 8; B200_ERR_UNSUPPORTED otherwise)
+int launch_gemm_tc_grouped(const void *a, const void *w, void *c, int max_rows, int N, int K, int experts, const int *tile_expert,
+                           const int *n_live, int act, int dtype, cudaStream_t st);
 // c[row, n] = act?(sum_k a[row, k] * w[tile_expert[row / kMoeTileM]][n, k]);  rows >= n_tiles * kMoeTileM are skipped
 int launch_moe_grouped_gemm(int dtype, const void *a, const void *w, void *c, const int *tile_expert, const int *n_tiles, int max_tiles,
                             int N, int K, int act, cudaStream_t st);

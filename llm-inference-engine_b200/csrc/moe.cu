@@ -1,4 +1,5 @@
-// moe.cu -- mixture-of-experts feed-forward for ragged token batches.
+// moe.cu -- mixture-of-experts feed-forward for ragged token batches.  (Row tiles are 64 rows for the kernels of this file, 128 for the
+// tcgen05 grouped GEMM of gemm_tc.cu, which serves prompt-sized batches of 16-bit engines; the engine chooses per call.)
 //   route:   scores = sigmoid(router logits) (fp32); the `top` largest are chosen, their scores ARE the weights (no renormalisation);
 //            a separate sigmoid gate scales the shared expert.
 //   plan:    the (token, choice) pairs are grouped by expert; every expert's rows are padded to whole tiles of kMoeTileM rows so that a
@@ -10,16 +11,6 @@
 #include "hybrid_ops.cuh"
 
 namespace b200 {
-
-__device__ __forceinline__ float act_apply(float v, int act) {
-    if (act == B200_ACT_RELU2) {
-        const float r = fmaxf(v, 0.0f);
-        return r * r;
-    }
-    if (act == B200_ACT_SILU) return v / (1.0f + expf(-v));
-    const float c = 0.7978845608028654f;  // sqrt(2/pi)
-    return 0.5f * v * (1.0f + tanhf(c * (v + 0.044715f * v * v * v)));
-}
 
 // one warp per token
 __global__ void moe_route_sigmoid_kernel(const float *__restrict__ logits, int ld, int *__restrict__ sel_expert, float *__restrict__ sel_weight,
@@ -53,7 +44,7 @@ __global__ void moe_route_sigmoid_kernel(const float *__restrict__ logits, int l
 // one CTA.  Shared: count[E] | offset[E+1] | cursor[E]
 __global__ void __launch_bounds__(1024)
 moe_plan_kernel(const int *__restrict__ sel_expert, const float *__restrict__ sel_weight, int *__restrict__ row_token, float *__restrict__ row_weight,
-                int *__restrict__ tile_expert, int *__restrict__ pair_row, int *__restrict__ n_tiles, int pairs, int experts, int top) {
+                int *__restrict__ tile_expert, int *__restrict__ pair_row, int *__restrict__ n_tiles, int pairs, int experts, int top, int tile) {
     extern __shared__ int si[];
     int *count = si, *offset = si + experts, *cursor = offset + experts + 1;
     for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0, cursor[e] = 0;
@@ -64,12 +55,12 @@ moe_plan_kernel(const int *__restrict__ sel_expert, const float *__restrict__ se
         int at = 0;
         for (int e = 0; e < experts; ++e) {
             offset[e] = at;
-            const int tiles = (count[e] + kMoeTileM - 1) / kMoeTileM;
-            for (int i = 0; i < tiles; ++i) tile_expert[at / kMoeTileM + i] = e;
-            at += tiles * kMoeTileM;
+            const int tiles = (count[e] + tile - 1) / tile;
+            for (int i = 0; i < tiles; ++i) tile_expert[at / tile + i] = e;
+            at += tiles * tile;
         }
         offset[experts] = at;
-        *n_tiles = at / kMoeTileM;
+        *n_tiles = at / tile;
     }
     __syncthreads();
     const int rows = offset[experts];
@@ -87,9 +78,9 @@ moe_plan_kernel(const int *__restrict__ sel_expert, const float *__restrict__ se
 template <typename T>
 __global__ void __launch_bounds__(128)
 moe_gather_kernel(const float *__restrict__ x, const int *__restrict__ row_token, const float *__restrict__ row_weight, T *__restrict__ xg,
-                  const int *__restrict__ n_tiles, int width) {
+                  const int *__restrict__ n_tiles, int width, int tile) {
     const int r = blockIdx.x;
-    if (r >= *n_tiles * kMoeTileM) return;
+    if (r >= *n_tiles * tile) return;
     const int t = row_token[r];
     const float w = row_weight[r];
     for (int c = threadIdx.x; c < width; c += blockDim.x)
@@ -268,17 +259,16 @@ int launch_moe_route_sigmoid(const float *logits, int ld, int *sel_expert, float
 }
 
 int launch_moe_plan(const int *sel_expert, const float *sel_weight, int *row_token, float *row_weight, int *tile_expert, int *pair_row,
-                    int *n_tiles, int tokens, int experts, int top, int max_rows, cudaStream_t st) {
-    (void)max_rows;
+                    int *n_tiles, int tokens, int experts, int top, int tile, cudaStream_t st) {
     moe_plan_kernel<<<1, 1024, (size_t)(3 * experts + 1) * sizeof(int), st>>>(sel_expert, sel_weight, row_token, row_weight, tile_expert,
-                                                                             pair_row, n_tiles, tokens * top, experts, top);
+                                                                             pair_row, n_tiles, tokens * top, experts, top, tile);
     return cuda_status("moe_plan launch");
 }
 
 int launch_moe_gather(int dtype, const float *x, const int *row_token, const float *row_weight, void *xg, const int *n_tiles,
-                      int max_rows, int width, cudaStream_t st) {
+                      int max_rows, int width, int tile, cudaStream_t st) {
     if (max_rows == 0) return B200_OK;
-    B200_DISPATCH_DTYPE(dtype, { moe_gather_kernel<T><<<max_rows, 128, 0, st>>>(x, row_token, row_weight, (T *)xg, n_tiles, width); });
+    B200_DISPATCH_DTYPE(dtype, { moe_gather_kernel<T><<<max_rows, 128, 0, st>>>(x, row_token, row_weight, (T *)xg, n_tiles, width, tile); });
     return cuda_status("moe_gather launch");
 }
 

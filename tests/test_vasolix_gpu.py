@@ -450,3 +450,22 @@ def test_bf16_engine_with_tensor_core_attention_in_portions():
     for name in req:
         per_pos = np.linalg.norm(got[name] - want[name], axis=-1) / np.linalg.norm(want[name], axis=-1)
         assert np.median(per_pos) < 3e-2 and per_pos.max() < 0.15, (name, float(np.median(per_pos)), float(per_pos.max()))
+
+
+def test_prompt_sized_expert_batches_take_the_tcgen05_grouped_gemm():
+    """More than a thousand (token, expert) pairs in a 16-bit engine: the experts run as 128-row tiles on the tcgen05 grouped GEMM.  Every
+    expert is chosen for every token here (no close routing calls), so the result must agree with the float64 model to 16-bit rounding and
+    with the same prompt fed in portions small enough to take the 64-row mma.sync kernel."""
+    layers = [ref.gla_layer(heads=2, dim=16, vdim=32, mlp=ref.moe(experts=4, top=4, ff=64, shared_ff=72)),
+              ref.attention_layer(heads=2, kv_heads=1, dim=64, size=300, scale=0.125, mlp=ref.moe(experts=3, top=3, ff=136, shared_ff=64))]
+    config = ref.make_config(layers, width=64)
+    W, packed = ref.make_weights(config, seed=71)
+    req = {"a": tokens_of(config, 700, 9)}
+    want = want_logits(config, W, req["a"])
+    for dtype in ("bfloat16", "float16"):
+        whole = replay(session(config, packed, dtype=dtype, pool_tokens=768, max_batch_tokens=768), req, [[("a", 700)]])["a"]
+        parts = replay(session(config, packed, dtype=dtype, pool_tokens=768, max_batch_tokens=768), req, [[("a", 100)]] * 7)["a"]
+        per_pos = np.linalg.norm(whole - want, axis=-1) / np.linalg.norm(want, axis=-1)
+        assert np.median(per_pos) < 3e-2 and per_pos.max() < 0.15, (dtype, float(np.median(per_pos)), float(per_pos.max()))
+        same = np.linalg.norm(whole - parts, axis=-1) / np.linalg.norm(want, axis=-1)
+        assert np.median(same) < 1.5e-2 and same.max() < 0.1, (dtype, float(np.median(same)), float(same.max()))
