@@ -203,7 +203,7 @@ gla_recurrent_reg_kernel(const T *__restrict__ proj, int ld, const float *__rest
                 }
             };
             // butterfly over the 32 lanes, halving the columns a lane is responsible for: 8 -> 4 -> 2 -> 1, then two plain steps
-            auto reduce_store = [&](const float *acc, int t) {
+            auto reduce = [&](const float *acc) -> float {
                 float a4[4], a2[2], a1;
                 {
                     const bool up = lane & 16;
@@ -228,22 +228,30 @@ gla_recurrent_reg_kernel(const T *__restrict__ proj, int ld, const float *__rest
                 }
                 a1 += __shfl_xor_sync(0xffffffffu, a1, 2);
                 a1 += __shfl_xor_sync(0xffffffffu, a1, 1);
-                // lane l now holds column ((l >> 4) & 1) * 4 + ((l >> 3) & 1) * 2 + ((l >> 2) & 1) of the warp's eight
-                const int c = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
-                if ((lane & 3) == 0 && c0 + c < vdim) o[((size_t)t * heads + h) * vdim + c0 + c] = a1;
+                return a1;  // every lane of a group of four holds column ((l >> 4) & 1) * 4 + ((l >> 3) & 1) * 2 + ((l >> 2) & 1)
             };
-            // the reduction of token t - 1 sits in the same straight-line code as the multiply-adds of token t: its shuffle latency is
-            // covered by them
-            float pacc[kGlaWarpCols], acc[kGlaWarpCols];
-            advance(0, pacc);
-#pragma unroll 2
-            for (int tt = 1; tt < nt; ++tt) {
-                advance(tt, acc);
-                reduce_store(pacc, tb + tt - 1);
+            const int ocol = c0 + ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+            // tokens in groups of four: the four updates of S are a short serial chain, the four reductions are independent of one
+            // another and sit in one straight-line block, so their shuffle latencies overlap instead of adding up per token
+            int tt = 0;
+            for (; tt + 4 <= nt; tt += 4) {
+                float acc4[4][kGlaWarpCols];
 #pragma unroll
-                for (int c = 0; c < kGlaWarpCols; ++c) pacc[c] = acc[c];
+                for (int u = 0; u < 4; ++u) advance(tt + u, acc4[u]);
+                float r4[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) r4[u] = reduce(acc4[u]);
+                // lane l of a group of four stores token (l & 3): one store per lane for the four tokens, no branch per token
+                const int u = lane & 3;
+                const float val = u == 0 ? r4[0] : (u == 1 ? r4[1] : (u == 2 ? r4[2] : r4[3]));
+                if (ocol < vdim) o[((size_t)(tb + tt + u) * heads + h) * vdim + ocol] = val;
             }
-            reduce_store(pacc, tb + nt - 1);
+            for (; tt < nt; ++tt) {
+                float acc[kGlaWarpCols];
+                advance(tt, acc);
+                const float val = reduce(acc);
+                if ((lane & 3) == 0 && ocol < vdim) o[((size_t)(tb + tt) * heads + h) * vdim + ocol] = val;
+            }
         }
         __syncthreads();  // the next stage is filled and this one consumed
     }
