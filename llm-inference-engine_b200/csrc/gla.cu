@@ -231,20 +231,24 @@ gla_recurrent_reg_kernel(const T *__restrict__ proj, int ld, const float *__rest
                 return a1;  // every lane of a group of four holds column ((l >> 4) & 1) * 4 + ((l >> 3) & 1) * 2 + ((l >> 2) & 1)
             };
             const int ocol = c0 + ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
-            // tokens in groups of four: the four updates of S are a short serial chain, the four reductions are independent of one
+            // tokens in groups: the updates of S are a short serial chain, the reductions are independent of one
             // another and sit in one straight-line block, so their shuffle latencies overlap instead of adding up per token
             int tt = 0;
-            for (; tt + 4 <= nt; tt += 4) {
-                float acc4[4][kGlaWarpCols];
+            constexpr int GS = 8;  // tokens per group
+            for (; tt + GS <= nt; tt += GS) {
+                float accg[GS][kGlaWarpCols];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) advance(tt + u, acc4[u]);
-                float r4[4];
+                for (int u = 0; u < GS; ++u) advance(tt + u, accg[u]);
+                float rg[GS];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) r4[u] = reduce(acc4[u]);
-                // lane l of a group of four stores token (l & 3): one store per lane for the four tokens, no branch per token
+                for (int u = 0; u < GS; ++u) rg[u] = reduce(accg[u]);
+                // lane l of a group of four stores tokens (l & 3), (l & 3) + 4: no branch per token
                 const int u = lane & 3;
-                const float val = u == 0 ? r4[0] : (u == 1 ? r4[1] : (u == 2 ? r4[2] : r4[3]));
-                if (ocol < vdim) o[((size_t)(tb + tt + u) * heads + h) * vdim + ocol] = val;
+#pragma unroll
+                for (int half = 0; half < GS / 4; ++half) {
+                    const float val = u == 0 ? rg[4 * half] : (u == 1 ? rg[4 * half + 1] : (u == 2 ? rg[4 * half + 2] : rg[4 * half + 3]));
+                    if (ocol < vdim) o[((size_t)(tb + tt + 4 * half + u) * heads + h) * vdim + ocol] = val;
+                }
             }
             for (; tt < nt; ++tt) {
                 float acc[kGlaWarpCols];
