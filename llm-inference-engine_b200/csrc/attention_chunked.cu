@@ -8,6 +8,8 @@
 // Scores, softmax and the weighted sum are fp32; q, k, v and the output are of the engine dtype.
 #include "hybrid_ops.cuh"
 
+#include <algorithm>
+
 namespace b200 {
 
 constexpr int kPage = B200_KV_PAGE_SIZE;
@@ -51,9 +53,9 @@ attn_qk_norm_cache_kernel(const T *__restrict__ proj, int ld, T *__restrict__ q_
     }
 }
 
-// One CTA per (token, query head).  Shared memory: q[dim] | scores[keys] | partial[groups][dim] | red[33].
+// One CTA per (token, query head).  Shared memory: q[dim] | scores[keys] | partial[key groups][dim] | red[33].
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 chunked_attn_kernel(const T *__restrict__ q, const T *__restrict__ k_pool, const T *__restrict__ v_pool, const float *__restrict__ sink,
                     const T *__restrict__ gate_in, int gate_ld, T *__restrict__ out, const int *__restrict__ tok_seq,
                     const int *__restrict__ tok_pos, const int *__restrict__ block_table, int mpps, int heads, int kv_heads, int dim,
@@ -68,7 +70,7 @@ chunked_attn_kernel(const T *__restrict__ q, const T *__restrict__ k_pool, const
     float *qs = sm;
     float *sc = qs + dim;
     float *part = sc + max_keys;
-    float *red = part + (size_t)ngroups * dim;
+    float *red = part + max((size_t)ngroups * dim, (size_t)blockDim.x * 8);
     const int *bt = block_table + (size_t)tok_seq[t] * mpps;
     for (int c = threadIdx.x; c < dim; c += blockDim.x) qs[c] = Elem<T>::to_f(q[((size_t)t * heads + h) * dim + c]);
     __syncthreads();
@@ -83,7 +85,8 @@ chunked_attn_kernel(const T *__restrict__ q, const T *__restrict__ k_pool, const
         float acc = 0.0f;
         if (vec) {
             constexpr int V = Elem<T>::kVec;
-            for (int c = 0; c < dim; c += V) {
+#pragma unroll 8
+            for (int c = 0; c < dim; c += V) {  // unrolled: a thread's loads of one key row are in flight together
                 float f[V];
                 unpack16<T>(ld_v4(kr + c), f);
 #pragma unroll
@@ -107,8 +110,38 @@ chunked_attn_kernel(const T *__restrict__ q, const T *__restrict__ k_pool, const
     if (sink) sum += expf(sink[h] - mx);
     const float inv = 1.0f / sum;
 
-    // ---- weighted sum of the values: column c by thread, keys dealt over `ngroups` thread groups
-    if (ngroups > 1) {
+    // ---- weighted sum of the values
+    constexpr int V = Elem<T>::kVec;
+    const int tpr = dim / V;  // threads per value row when a thread takes one 16-byte piece
+    if (vec && tpr <= (int)blockDim.x) {
+        // a thread owns V consecutive columns; the block walks blockDim / tpr keys at a time with 16-byte loads, then the key groups'
+        // partial sums meet in shared memory
+        const int groups = (int)blockDim.x / tpr, kg = threadIdx.x / tpr, c0 = (threadIdx.x - kg * tpr) * V;
+        float acc[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] = 0.0f;
+        if (kg < groups) {
+#pragma unroll 4
+            for (int j = kg; j < nkeys; j += groups) {
+                const int p = first + j;
+                const int page = bt[p / kPage];
+                float f[V];
+                unpack16<T>(ld_v4(v_pool + (((size_t)page * kv_heads + g) * kPage + (p % kPage)) * dim + c0), f);
+                const float w = sc[j];
+#pragma unroll
+                for (int i = 0; i < V; ++i) acc[i] = fmaf(w, f[i], acc[i]);
+            }
+#pragma unroll
+            for (int i = 0; i < V; ++i) part[kg * dim + c0 + i] = acc[i];
+        }
+        __syncthreads();
+        for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+            float a = 0.0f;
+            for (int k2 = 0; k2 < groups; ++k2) a += part[k2 * dim + c];
+            part[c] = a;  // column c's entries are read by this thread only
+        }
+        __syncthreads();
+    } else if (ngroups > 1) {
         const int kg = threadIdx.x / dim, c = threadIdx.x - kg * dim;
         if (kg < ngroups) {
             float acc = 0.0f;
@@ -395,9 +428,10 @@ int launch_chunked_attention(int dtype, const void *q, const void *k_pool, const
                              int gate_ld, void *out, const int *tok_seq, const int *tok_pos, const int *block_table, int mpps, int tokens,
                              int heads, int kv_heads, int dim, float scale, int chunk, int max_keys, cudaStream_t st, const int *tok_list) {
     if (tokens == 0) return B200_OK;
-    const int threads = 128;
+    const int threads = max_keys >= 256 ? 256 : 128;  // long chunks: more keys in flight per CTA
     const int ngroups = threads >= dim ? threads / dim : 1;
-    const size_t smem = ((size_t)dim + max_keys + (size_t)ngroups * dim + 33) * sizeof(float);
+    const size_t part = std::max((size_t)ngroups * dim, (size_t)threads * 8);  // key-group partial sums (scalar / 16-byte path)
+    const size_t smem = ((size_t)dim + max_keys + part + 33) * sizeof(float);
     if (smem > 200 * 1024) {
         set_error("chunked_attention: %d keys x dim %d do not fit the shared-memory score buffer", max_keys, dim);
         return B200_ERR_UNSUPPORTED;

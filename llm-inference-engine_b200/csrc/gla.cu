@@ -20,7 +20,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 gla_decay_kernel(const T *__restrict__ proj, int ld, int col0, const T *__restrict__ w, const float *__restrict__ bias, float inv_tau,
                  float *__restrict__ decay, int tokens, int rank, int channels) {
-    extern __shared__ float lo[];  // [kDecayTokens][rank]: the tokens' low-rank vectors
+    extern __shared__ __align__(16) float lo[];  // [kDecayTokens][rank]: the tokens' low-rank vectors
     const int t0 = blockIdx.x * kDecayTokens;
     const int nt = min(kDecayTokens, tokens - t0);
     for (int i = threadIdx.x; i < kDecayTokens * rank; i += blockDim.x) {
@@ -34,10 +34,22 @@ gla_decay_kernel(const T *__restrict__ proj, int ld, int col0, const T *__restri
 #pragma unroll
         for (int tt = 0; tt < kDecayTokens; ++tt) z[tt] = b0;
         const T *wr = w + (size_t)c * rank;
-        for (int r = 0; r < rank; ++r) {
-            const float wv = Elem<T>::to_f(wr[r]);
+        if ((rank & 3) == 0) {
+            // four ranks per shared-memory read (one 16-byte broadcast per token instead of four 4-byte ones)
+            for (int r = 0; r < rank; r += 4) {
+                const float w0 = Elem<T>::to_f(wr[r]), w1 = Elem<T>::to_f(wr[r + 1]), w2 = Elem<T>::to_f(wr[r + 2]), w3 = Elem<T>::to_f(wr[r + 3]);
 #pragma unroll
-            for (int tt = 0; tt < kDecayTokens; ++tt) z[tt] = fmaf(wv, lo[tt * rank + r], z[tt]);
+                for (int tt = 0; tt < kDecayTokens; ++tt) {
+                    const float4 l = *reinterpret_cast<const float4 *>(lo + tt * rank + r);
+                    z[tt] = fmaf(w3, l.w, fmaf(w2, l.z, fmaf(w1, l.y, fmaf(w0, l.x, z[tt]))));
+                }
+            }
+        } else {
+            for (int r = 0; r < rank; ++r) {
+                const float wv = Elem<T>::to_f(wr[r]);
+#pragma unroll
+                for (int tt = 0; tt < kDecayTokens; ++tt) z[tt] = fmaf(wv, lo[tt * rank + r], z[tt]);
+            }
         }
 #pragma unroll
         for (int tt = 0; tt < kDecayTokens; ++tt) {

@@ -1,5 +1,5 @@
 """Host-side parts of serving Vasolix, no GPU: the scheduler's state slots, portions and caller-driven sequences, the configuration
-reader, the checkpoint reader, the registry -- and the checker's own masks."""
+reader, the checkpoint reader, the registry -- and the oracle's own masks."""
 import importlib
 import json
 import struct
@@ -167,7 +167,7 @@ def test_end_id_finishes_a_sequence_in_the_mixed_plan():
 
 
 def test_checker_masks_and_sink():
-    """The checker itself: a key outside the query's block must not matter, the block's first key must, and the sink only scales."""
+    """The oracle itself: a key outside the query's block must not matter, the block's first key must, and the sink only scales."""
     config = ref.make_config([ref.attention_layer(heads=2, kv_heads=1, dim=8, size=10)])
     W, _ = ref.make_weights(config, seed=2)
     toks = np.random.default_rng(0).integers(0, 61, 25).tolist()

@@ -469,3 +469,20 @@ def test_prompt_sized_expert_batches_take_the_tcgen05_grouped_gemm():
         assert np.median(per_pos) < 3e-2 and per_pos.max() < 0.15, (dtype, float(np.median(per_pos)), float(per_pos.max()))
         same = np.linalg.norm(whole - parts, axis=-1) / np.linalg.norm(want, axis=-1)
         assert np.median(same) < 1.5e-2 and same.max() < 0.1, (dtype, float(np.median(same)), float(same.max()))
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 5e-5), ("bfloat16", 4e-2)])
+def test_sizes_that_fit_no_vector_or_tile(dtype, tol):
+    """Width, head sizes, expert sizes and ranks that are multiples of nothing convenient (not of 8, some not of 4, a chunk of 7, one kv
+    head, one gla head, three experts): every kernel's scalar / bounds path."""
+    layers = [ref.attention_layer(heads=3, kv_heads=1, dim=12, size=7, scale=0.4, mlp=ref.moe(experts=3, top=3, ff=10, shared_ff=6)),
+              ref.gla_layer(heads=1, dim=20, vdim=12, tau=3.0, mlp=ref.moe(experts=2, top=2, ff=9, shared_ff=5)),
+              ref.gla_layer(heads=5, dim=4, vdim=9, tau=1.5)]
+    config = ref.make_config(layers, width=52, vocab=37)
+    W, packed = ref.make_weights(config, seed=81, decay_rank=5)
+    req = {"a": tokens_of(config, 75, 1), "b": tokens_of(config, 20, 2)}
+    got = replay(session(config, packed, dtype=dtype), req, [[("a", 30), ("b", 2)], [("a", 1), ("b", 17)], [("a", 44), ("b", 1)]])
+    for name in req:
+        want = want_logits(config, W, req[name])
+        per_pos = np.linalg.norm(got[name] - want, axis=-1) / np.linalg.norm(want, axis=-1)
+        assert np.median(per_pos) < tol and per_pos.max() < 5 * tol, (name, float(np.median(per_pos)), float(per_pos.max()))

@@ -1,5 +1,5 @@
 """Plain, slow restatement of the Vasolix design in float64 on the CPU, one function per mechanism, written from the design's
-equations and sharing nothing with the package: the checker for tests/test_vasolix*.py.
+equations and sharing nothing with the package: the oracle for tests/test_vasolix*.py.
 
 Notation: h is a [T, width] block of one sequence's tokens at positions 0..T-1; W['name'] are float64 matrices stored [out, in].
 Every function sees the WHOLE sequence at once (no cache, no state carried between calls): whatever the engine does with pages, slots,
@@ -124,7 +124,7 @@ def make_config(layers, width=48, vocab=61, eps=1e-5):
 
 def make_weights(config, seed=0, decay_rank=6):
     """Random tensors with the checkpoint's names, every value exactly representable in bfloat16 (so that a bf16 engine, an fp32 engine and
-    this float64 checker all hold the same model).  Returns (float64 dict for the checker, bf16 dict for the package)."""
+    this float64 oracle all hold the same model).  Returns (float64 dict for the oracle, bf16 dict for the package)."""
     g = torch.Generator().manual_seed(seed)
     width, vocab = config["width"], config["vocab"]
     t = {}
