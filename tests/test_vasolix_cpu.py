@@ -166,7 +166,7 @@ def test_end_id_finishes_a_sequence_in_the_mixed_plan():
     assert state == m.REQ_FINISHED and ids.tolist() == [11, 11, 11, 7]
 
 
-def test_checker_masks_and_sink():
+def test_oracle_masks_and_sink():
     """The oracle itself: a key outside the query's block must not matter, the block's first key must, and the sink only scales."""
     config = ref.make_config([ref.attention_layer(heads=2, kv_heads=1, dim=8, size=10)])
     W, _ = ref.make_weights(config, seed=2)
