@@ -75,29 +75,62 @@ chunked_attn_kernel(const T *__restrict__ q, const T *__restrict__ k_pool, const
     for (int c = threadIdx.x; c < dim; c += blockDim.x) qs[c] = Elem<T>::to_f(q[((size_t)t * heads + h) * dim + c]);
     __syncthreads();
 
-    // ---- scores: one key per thread
+    // ---- scores: four adjacent lanes share a key row (each takes every fourth 16-byte piece, so a warp's load covers whole 64-byte
+    // segments of eight rows and a short chunk still spreads over the block); other head sizes: one key per thread
     const bool vec = (dim % Elem<T>::kVec) == 0;
     float mx = sink ? sink[h] : -INFINITY;
-    for (int j = threadIdx.x; j < nkeys; j += blockDim.x) {
-        const int p = first + j;
-        const int page = bt[p / kPage];
-        const T *kr = k_pool + (((size_t)page * kv_heads + g) * kPage + (p % kPage)) * dim;
-        float acc = 0.0f;
-        if (vec) {
-            constexpr int V = Elem<T>::kVec;
-#pragma unroll 8
-            for (int c = 0; c < dim; c += V) {  // unrolled: a thread's loads of one key row are in flight together
+    if (dim % (4 * Elem<T>::kVec) == 0 && blockDim.x % 32 == 0) {
+        constexpr int V = Elem<T>::kVec;
+        const int sub = threadIdx.x & 3, kslot = threadIdx.x >> 2, nslots = blockDim.x >> 2, pieces = dim / V;
+#pragma unroll 2
+        for (int j0 = 0; j0 < nkeys; j0 += nslots) {  // warp-uniform trip count: the shuffles below take every lane
+            const int j = j0 + kslot;
+            const int p = first + min(j, nkeys - 1);
+            const int page = bt[p / kPage];
+            const T *kr = k_pool + (((size_t)page * kv_heads + g) * kPage + (p % kPage)) * dim;
+            float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll 4
+            for (int pc = sub; pc < pieces; pc += 4) {
                 float f[V];
-                unpack16<T>(ld_v4(kr + c), f);
+                unpack16<T>(ld_v4(kr + pc * V), f);
+                const float *qp = qs + pc * V;
 #pragma unroll
-                for (int i = 0; i < V; ++i) acc = fmaf(qs[c + i], f[i], acc);
+                for (int i = 0; i < V; i += 2) {
+                    a0 = fmaf(qp[i], f[i], a0);
+                    a1 = fmaf(qp[i + 1], f[i + 1], a1);
+                }
             }
-        } else {
-            for (int c = 0; c < dim; ++c) acc = fmaf(qs[c], Elem<T>::to_f(kr[c]), acc);
+            float acc = a0 + a1;
+            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            acc *= scale;
+            if (j < nkeys) {
+                if (sub == 0) sc[j] = acc;
+                mx = fmaxf(mx, acc);
+            }
         }
-        acc *= scale;
-        sc[j] = acc;
-        mx = fmaxf(mx, acc);
+    } else {
+        for (int j = threadIdx.x; j < nkeys; j += blockDim.x) {
+            const int p = first + j;
+            const int page = bt[p / kPage];
+            const T *kr = k_pool + (((size_t)page * kv_heads + g) * kPage + (p % kPage)) * dim;
+            float acc = 0.0f;
+            if (vec) {
+                constexpr int V = Elem<T>::kVec;
+#pragma unroll 8
+                for (int c = 0; c < dim; c += V) {  // unrolled: a thread's loads of one key row are in flight together
+                    float f[V];
+                    unpack16<T>(ld_v4(kr + c), f);
+#pragma unroll
+                    for (int i = 0; i < V; ++i) acc = fmaf(qs[c + i], f[i], acc);
+                }
+            } else {
+                for (int c = 0; c < dim; ++c) acc = fmaf(qs[c], Elem<T>::to_f(kr[c]), acc);
+            }
+            acc *= scale;
+            sc[j] = acc;
+            mx = fmaxf(mx, acc);
+        }
     }
     mx = block_max(mx, red);
     float sum = 0.0f;
@@ -121,7 +154,7 @@ chunked_attn_kernel(const T *__restrict__ q, const T *__restrict__ k_pool, const
 #pragma unroll
         for (int i = 0; i < V; ++i) acc[i] = 0.0f;
         if (kg < groups) {
-#pragma unroll 4
+#pragma unroll 8
             for (int j = kg; j < nkeys; j += groups) {
                 const int p = first + j;
                 const int page = bt[p / kPage];

@@ -27,6 +27,7 @@ gla_decay_kernel(const T *__restrict__ proj, int ld, int col0, const T *__restri
         const int tt = i / rank, r = i - tt * rank;
         lo[i] = tt < nt ? Elem<T>::to_f(proj[(size_t)(t0 + tt) * ld + col0 + r]) : 0.0f;
     }
+    const bool vec_w = rank % Elem<T>::kVec == 0 && (reinterpret_cast<size_t>(w) & 15) == 0;
     __syncthreads();
     for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
         float z[kDecayTokens];
@@ -34,14 +35,19 @@ gla_decay_kernel(const T *__restrict__ proj, int ld, int col0, const T *__restri
 #pragma unroll
         for (int tt = 0; tt < kDecayTokens; ++tt) z[tt] = b0;
         const T *wr = w + (size_t)c * rank;
-        if ((rank & 3) == 0) {
-            // four ranks per shared-memory read (one 16-byte broadcast per token instead of four 4-byte ones)
-            for (int r = 0; r < rank; r += 4) {
-                const float w0 = Elem<T>::to_f(wr[r]), w1 = Elem<T>::to_f(wr[r + 1]), w2 = Elem<T>::to_f(wr[r + 2]), w3 = Elem<T>::to_f(wr[r + 3]);
+        if (vec_w) {
+            // a row of the matrix in 16-byte pieces; four ranks per shared-memory read (one 16-byte broadcast per token)
+            constexpr int V = Elem<T>::kVec;
+            for (int r = 0; r < rank; r += V) {
+                float wv[V];
+                unpack16<T>(ld_v4(wr + r), wv);
 #pragma unroll
-                for (int tt = 0; tt < kDecayTokens; ++tt) {
-                    const float4 l = *reinterpret_cast<const float4 *>(lo + tt * rank + r);
-                    z[tt] = fmaf(w3, l.w, fmaf(w2, l.z, fmaf(w1, l.y, fmaf(w0, l.x, z[tt]))));
+                for (int q4 = 0; q4 < V; q4 += 4) {
+#pragma unroll
+                    for (int tt = 0; tt < kDecayTokens; ++tt) {
+                        const float4 l = *reinterpret_cast<const float4 *>(lo + tt * rank + r + q4);
+                        z[tt] = fmaf(wv[q4 + 3], l.w, fmaf(wv[q4 + 2], l.z, fmaf(wv[q4 + 1], l.y, fmaf(wv[q4], l.x, z[tt]))));
+                    }
                 }
             }
         } else {
@@ -67,7 +73,7 @@ template <typename T>
 __global__ void __launch_bounds__(kGlaThreads)
 gla_recurrent_kernel(const T *__restrict__ proj, int ld, const float *__restrict__ decay, float *__restrict__ state, float *__restrict__ o,
                      const int *__restrict__ seq_start, const int *__restrict__ seq_pos0, const int *__restrict__ seq_slot, int heads,
-                     int dim, int vdim) {
+                     int dim, int vdim, int min_tokens) {
     extern __shared__ float sm[];
     float *S = sm;
     float *qs = S + (size_t)dim * kGlaCols;
@@ -79,7 +85,7 @@ gla_recurrent_kernel(const T *__restrict__ proj, int ld, const float *__restrict
     const int col = threadIdx.x % kGlaCols, rg = threadIdx.x / kGlaCols;
     constexpr int kRowGroups = kGlaThreads / kGlaCols;
     const int t0 = seq_start[s], t1 = seq_start[s + 1];
-    if (t1 <= t0) return;
+    if (t1 - t0 < min_tokens) return;
     const bool live = j0 + col < vdim;
     float *slot = state + (((size_t)seq_slot[s] * heads + h) * dim) * vdim;
     const bool fresh = seq_pos0[s] == 0;
@@ -127,7 +133,7 @@ template <typename T, int RR, int TB>
 __global__ void __launch_bounds__(256)
 gla_recurrent_reg_kernel(const T *__restrict__ proj, int ld, const float *__restrict__ decay, float *__restrict__ state, float *__restrict__ o,
                          const int *__restrict__ seq_start, const int *__restrict__ seq_pos0, const int *__restrict__ seq_slot, int heads,
-                         int dim, int vdim) {
+                         int dim, int vdim, int min_tokens) {
     extern __shared__ __align__(16) float smf[];
     constexpr int DP = 32 * RR;                                  // padded rows
     constexpr int kStage = TB * DP * 4 + TB * kGlaCols;          // floats per stage: {a, k, q, -} [TB][DP] | v [TB][32]
@@ -138,7 +144,7 @@ gla_recurrent_reg_kernel(const T *__restrict__ proj, int ld, const float *__rest
     const bool producer = warp >= 4;                             // warps 4..7 stage the next block of tokens while warps 0..3 compute
     const int c0 = j0 + (warp & 3) * kGlaWarpCols;
     const int t0 = seq_start[s], t1 = seq_start[s + 1];
-    if (t1 <= t0) return;
+    if (t1 - t0 < min_tokens) return;
     float *slot = state + (((size_t)seq_slot[s] * heads + h) * dim) * vdim;
     const bool fresh = seq_pos0[s] == 0;
     const float qscale = rsqrtf((float)dim);
@@ -281,12 +287,84 @@ gla_recurrent_reg_kernel(const T *__restrict__ proj, int ld, const float *__rest
         }
 }
 
+// One-token portions (decoding): the step is a single pass over the sequence's state, so the kernel is laid out for the memory system
+// instead of the token loop.  A CTA owns kStepCols columns of one (sequence, head); a thread owns four consecutive columns (one 16-byte
+// piece of a state row) and every 16th row, the loads of a thread's rows are issued together, and the 16 row groups' partial outputs meet
+// in shared memory.  Sequences with more than one token leave at once (the token-loop kernel serves them) and vice versa.
+constexpr int kStepCols = 64;
+constexpr int kStepRowGroups = 16;
+constexpr int kStepUnroll = 8;
+template <typename T>
+__global__ void __launch_bounds__(256)
+gla_step_kernel(const T *__restrict__ proj, int ld, const float *__restrict__ decay, float *__restrict__ state, float *__restrict__ o,
+                const int *__restrict__ seq_start, const int *__restrict__ seq_pos0, const int *__restrict__ seq_slot, int heads, int dim,
+                int vdim) {
+    extern __shared__ __align__(16) float smf[];  // {a, k, q, -}[dim] | part[kStepRowGroups][kStepCols]
+    const int s = blockIdx.z, h = blockIdx.y, j0 = blockIdx.x * kStepCols;
+    const int t = seq_start[s];
+    if (seq_start[s + 1] - t != 1) return;
+    float4 *akq = reinterpret_cast<float4 *>(smf);
+    float *part = smf + 4 * (size_t)dim;
+    const T *row = proj + (size_t)t * ld;
+    const float qscale = rsqrtf((float)dim);
+    for (int i = threadIdx.x; i < dim; i += blockDim.x)
+        akq[i] = make_float4(decay[((size_t)t * heads + h) * dim + i], Elem<T>::to_f(row[heads * dim + h * dim + i]),
+                             Elem<T>::to_f(row[h * dim + i]) * qscale, 0.0f);
+    const int cg = threadIdx.x % (kStepCols / 4), rg = threadIdx.x / (kStepCols / 4);
+    const int c = j0 + 4 * cg;
+    const bool live = c < vdim;  // vdim is a multiple of 4 here
+    const bool fresh = seq_pos0[s] == 0;
+    float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (live) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[e] = Elem<T>::to_f(row[2 * heads * dim + h * vdim + c + e]);
+    }
+    float *slot = state + (((size_t)seq_slot[s] * heads + h) * dim) * vdim + c;
+    __syncthreads();
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (live) {
+        for (int i0 = rg; i0 < dim; i0 += kStepRowGroups * kStepUnroll) {
+            float4 sv[kStepUnroll];
+#pragma unroll
+            for (int u = 0; u < kStepUnroll; ++u) {
+                const int i = i0 + u * kStepRowGroups;
+                sv[u] = (!fresh && i < dim) ? *reinterpret_cast<const float4 *>(slot + (size_t)i * vdim) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+#pragma unroll
+            for (int u = 0; u < kStepUnroll; ++u) {
+                const int i = i0 + u * kStepRowGroups;
+                if (i < dim) {
+                    const float4 x = akq[i];
+                    float4 n;
+                    n.x = fmaf(x.x, sv[u].x, x.y * v[0]);
+                    n.y = fmaf(x.x, sv[u].y, x.y * v[1]);
+                    n.z = fmaf(x.x, sv[u].z, x.y * v[2]);
+                    n.w = fmaf(x.x, sv[u].w, x.y * v[3]);
+                    *reinterpret_cast<float4 *>(slot + (size_t)i * vdim) = n;
+                    acc[0] = fmaf(n.x, x.z, acc[0]);
+                    acc[1] = fmaf(n.y, x.z, acc[1]);
+                    acc[2] = fmaf(n.z, x.z, acc[2]);
+                    acc[3] = fmaf(n.w, x.z, acc[3]);
+                }
+            }
+        }
+    }
+    *reinterpret_cast<float4 *>(part + rg * kStepCols + 4 * cg) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    __syncthreads();
+    if (threadIdx.x < kStepCols && j0 + threadIdx.x < vdim) {
+        float r = 0.0f;
+#pragma unroll
+        for (int g = 0; g < kStepRowGroups; ++g) r += part[g * kStepCols + threadIdx.x];
+        o[((size_t)t * heads + h) * vdim + j0 + threadIdx.x] = r;
+    }
+}
+
 template <typename T, int RR, int TB>
 static void launch_gla_reg(const void *proj, int ld, const float *decay, float *state, float *o, const int *seq_start, const int *seq_pos0,
-                           const int *seq_slot, dim3 grid, int heads, int dim, int vdim, cudaStream_t st) {
+                           const int *seq_slot, dim3 grid, int heads, int dim, int vdim, int min_tokens, cudaStream_t st) {
     const size_t smem = 2 * ((size_t)TB * 32 * RR * 4 + (size_t)TB * kGlaCols) * sizeof(float);
     if (smem > 48 * 1024) cudaFuncSetAttribute(gla_recurrent_reg_kernel<T, RR, TB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    gla_recurrent_reg_kernel<T, RR, TB><<<grid, 256, smem, st>>>((const T *)proj, ld, decay, state, o, seq_start, seq_pos0, seq_slot, heads, dim, vdim);
+    gla_recurrent_reg_kernel<T, RR, TB><<<grid, 256, smem, st>>>((const T *)proj, ld, decay, state, o, seq_start, seq_pos0, seq_slot, heads, dim, vdim, min_tokens);
 }
 
 template <typename T>
@@ -321,8 +399,21 @@ int launch_gla_decay(int dtype, const void *proj, int ld, int col0, const void *
 }
 
 int launch_gla_recurrent(int dtype, const void *proj, int ld, const float *decay, float *state, float *o, const int *seq_start,
-                         const int *seq_pos0, const int *seq_slot, int n_seqs, int heads, int dim, int vdim, cudaStream_t st) {
+                         const int *seq_pos0, const int *seq_slot, int n_seqs, int heads, int dim, int vdim, cudaStream_t st, int kinds) {
     if (n_seqs == 0) return B200_OK;
+    // one-token portions take the step kernel (16-byte pieces of state rows: vdim a multiple of 4); the token-loop kernels then skip them
+    const bool step = (kinds & kGlaOneToken) && vdim % 4 == 0 && (reinterpret_cast<size_t>(state) & 15) == 0 &&
+                      (4 * (size_t)dim + kStepRowGroups * kStepCols) * sizeof(float) <= 200 * 1024;
+    if (step) {
+        const size_t smem_step = (4 * (size_t)dim + kStepRowGroups * kStepCols) * sizeof(float);
+        const dim3 grid_step((vdim + kStepCols - 1) / kStepCols, heads, n_seqs);
+        B200_DISPATCH_DTYPE(dtype, {
+            if (smem_step > 48 * 1024) cudaFuncSetAttribute(gla_step_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_step);
+            gla_step_kernel<T><<<grid_step, 256, smem_step, st>>>((const T *)proj, ld, decay, state, o, seq_start, seq_pos0, seq_slot, heads, dim, vdim);
+        });
+        if (!(kinds & kGlaManyTokens)) return cuda_status("gla_step launch");
+    }
+    const int min_tokens = step ? 2 : 1;
     const size_t smem = ((size_t)dim * kGlaCols + 3 * (size_t)dim + kGlaCols + (kGlaThreads / kGlaCols) * kGlaCols) * sizeof(float);
     if (smem > 200 * 1024) {
         set_error("gla_recurrent: key size %d does not fit the shared-memory state tile", dim);
@@ -331,17 +422,17 @@ int launch_gla_recurrent(int dtype, const void *proj, int ld, const float *decay
     const dim3 grid((vdim + kGlaCols - 1) / kGlaCols, heads, n_seqs);
     if (dim <= 256) {
         B200_DISPATCH_DTYPE(dtype, {
-            if (dim <= 32) launch_gla_reg<T, 1, 16>(proj, ld, decay, state, o, seq_start, seq_pos0, seq_slot, grid, heads, dim, vdim, st);
-            else if (dim <= 64) launch_gla_reg<T, 2, 16>(proj, ld, decay, state, o, seq_start, seq_pos0, seq_slot, grid, heads, dim, vdim, st);
-            else if (dim <= 128) launch_gla_reg<T, 4, 16>(proj, ld, decay, state, o, seq_start, seq_pos0, seq_slot, grid, heads, dim, vdim, st);
-            else launch_gla_reg<T, 8, 8>(proj, ld, decay, state, o, seq_start, seq_pos0, seq_slot, grid, heads, dim, vdim, st);
+            if (dim <= 32) launch_gla_reg<T, 1, 16>(proj, ld, decay, state, o, seq_start, seq_pos0, seq_slot, grid, heads, dim, vdim, min_tokens, st);
+            else if (dim <= 64) launch_gla_reg<T, 2, 16>(proj, ld, decay, state, o, seq_start, seq_pos0, seq_slot, grid, heads, dim, vdim, min_tokens, st);
+            else if (dim <= 128) launch_gla_reg<T, 4, 16>(proj, ld, decay, state, o, seq_start, seq_pos0, seq_slot, grid, heads, dim, vdim, min_tokens, st);
+            else launch_gla_reg<T, 8, 8>(proj, ld, decay, state, o, seq_start, seq_pos0, seq_slot, grid, heads, dim, vdim, min_tokens, st);
         });
         return cuda_status("gla_recurrent launch");
     }
     B200_DISPATCH_DTYPE(dtype, {
         if (smem > 48 * 1024) cudaFuncSetAttribute(gla_recurrent_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         gla_recurrent_kernel<T><<<grid, kGlaThreads, smem, st>>>((const T *)proj, ld, decay, state, o, seq_start, seq_pos0, seq_slot, heads, dim,
-                                                                  vdim);
+                                                                  vdim, min_tokens);
     });
     return cuda_status("gla_recurrent launch");
 }

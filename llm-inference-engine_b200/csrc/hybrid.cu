@@ -416,9 +416,10 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
         *h_start = h_short + NT, *h_pos0 = h_start + S + 1, *h_slot = h_pos0 + S, *h_bt = h_slot + S;
     // prompt portions go to the tensor-core attention in tiles of <= 64 consecutive tokens, short ones (decoded tokens) to the per-token kernel
     constexpr int kShortPortion = 8;
-    int n_tiles = 0, n_short = 0;
+    int n_tiles = 0, n_short = 0, gla_kinds = 0;
     for (int s = 0; s < S; ++s) {
         const int t0 = b->seq_start[s], t1 = b->seq_start[s + 1];
+        gla_kinds |= t1 - t0 == 1 ? kGlaOneToken : (t1 - t0 > 1 ? kGlaManyTokens : 0);
         B200_REQUIRE(t1 >= t0 && b->seq_pos0[s] >= 0, "hybrid_forward: bad portion of sequence %d", s);
         B200_REQUIRE(b->seq_slot[s] >= 0 && b->seq_slot[s] < m->num_slots, "hybrid_forward: state slot %d outside [0, %d)", b->seq_slot[s], m->num_slots);
         for (int s2 = 0; s2 < s; ++s2) B200_REQUIRE(b->seq_slot[s2] != b->seq_slot[s], "hybrid_forward: state slot %d given to two sequences", b->seq_slot[s]);
@@ -505,7 +506,7 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
             const char *gate = (const char *)m->proj + (size_t)(2 * hd + hv) * es;
             RUN(launch_gla_decay(dt, m->proj, lp.n_in, 2 * hd + 2 * hv, l.w_decay, l.decay_bias, l.tau, m->f32a, NT, l.decay_rank, hd, st));
             RUN(launch_gla_recurrent(dt, m->proj, lp.n_in, m->f32a, (float *)(m->state_pool + lp.state_off), m->f32b, d_start, d_pos0, d_slot, S,
-                                     l.heads, l.dim, l.vdim, st));
+                                     l.heads, l.dim, l.vdim, st, gla_kinds));
             RUN(launch_gla_output(dt, m->f32b, l.out_norm, c.norm_eps, gate, lp.n_in, m->mix2, NT, l.heads, l.vdim, st));
             RUN(linear(m, m->mix2, l.w_out, m->y, NT, hv, width, st));
         }

@@ -21,8 +21,11 @@ int launch_chunked_attention_tiles(int dtype, const void *q, const void *k_pool,
 // decay[t, c] = sigmoid(z)^(1/tau), z = w_decay[c, :] . proj[t, col0 : col0 + rank] + bias[c]   (fp32 from the projection on)
 int launch_gla_decay(int dtype, const void *proj, int ld, int col0, const void *w_decay, const float *bias, float tau, float *decay,
                      int tokens, int rank, int channels, cudaStream_t st);
+// kinds: which portions the batch holds, when the host knows (one-token portions have a kernel of their own; the default launches both)
+constexpr int kGlaOneToken = 1, kGlaManyTokens = 2;
 int launch_gla_recurrent(int dtype, const void *proj, int ld, const float *decay, float *state, float *o, const int *seq_start,
-                         const int *seq_pos0, const int *seq_slot, int n_seqs, int heads, int dim, int vdim, cudaStream_t st);
+                         const int *seq_pos0, const int *seq_slot, int n_seqs, int heads, int dim, int vdim, cudaStream_t st,
+                         int kinds = kGlaOneToken | kGlaManyTokens);
 // out[t, h*vdim + j] = o[t,h,j] * rsqrt(mean_j o^2 + eps) * w[j] * silu(gate[t*gate_ld + h*vdim + j])
 int launch_gla_output(int dtype, const float *o, const float *w, float eps, const void *gate_in, int gate_ld, void *out, int tokens,
                       int heads, int vdim, cudaStream_t st);
