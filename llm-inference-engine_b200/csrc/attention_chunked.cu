@@ -55,7 +55,7 @@ attn_qk_norm_cache_kernel(const T *__restrict__ proj, int ld, T *__restrict__ q_
 
 // One CTA per (token, query head).  Shared memory: q[dim] | scores[keys] | partial[key groups][dim] | red[33].
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(512)
 chunked_attn_kernel(const T *__restrict__ q, const T *__restrict__ k_pool, const T *__restrict__ v_pool, const float *__restrict__ sink,
                     const T *__restrict__ gate_in, int gate_ld, T *__restrict__ out, const int *__restrict__ tok_seq,
                     const int *__restrict__ tok_pos, const int *__restrict__ block_table, int mpps, int heads, int kv_heads, int dim,
@@ -461,7 +461,7 @@ int launch_chunked_attention(int dtype, const void *q, const void *k_pool, const
                              int gate_ld, void *out, const int *tok_seq, const int *tok_pos, const int *block_table, int mpps, int tokens,
                              int heads, int kv_heads, int dim, float scale, int chunk, int max_keys, cudaStream_t st, const int *tok_list) {
     if (tokens == 0) return B200_OK;
-    const int threads = max_keys >= 256 ? 256 : 128;  // long chunks: more keys in flight per CTA
+    const int threads = max_keys >= 512 ? 512 : (max_keys >= 256 ? 256 : 128);  // long chunks: more keys in flight per CTA
     const int ngroups = threads >= dim ? threads / dim : 1;
     const size_t part = std::max((size_t)ngroups * dim, (size_t)threads * 8);  // key-group partial sums (scalar / 16-byte path)
     const size_t smem = ((size_t)dim + max_keys + part + 33) * sizeof(float);

@@ -374,14 +374,43 @@ gla_output_kernel(const float *__restrict__ o, const float *__restrict__ w, floa
     __shared__ float red[33];
     const int t = blockIdx.x, h = blockIdx.y;
     const float *orow = o + ((size_t)t * heads + h) * vdim;
+    constexpr int V = Elem<T>::kVec;
+    const T *grow = gate_in + (size_t)t * gate_ld + h * vdim;
+    T *out_row = out + ((size_t)t * heads + h) * vdim;
+    // 16-byte pieces when every row starts on a 16-byte boundary
+    const bool vec = vdim % V == 0 && gate_ld % V == 0 && vdim <= (int)blockDim.x * V &&
+                     ((reinterpret_cast<size_t>(o) | reinterpret_cast<size_t>(w) | reinterpret_cast<size_t>(gate_in) | reinterpret_cast<size_t>(out)) & 15) == 0;
     float ss = 0.0f;
+    if (vec) {
+        float ov[V], gz[V];
+        const int j = threadIdx.x * V;  // the launcher gives a row's pieces one thread each
+        if (j < vdim) {
+#pragma unroll
+            for (int e = 0; e < V; e += 4) {
+                const float4 a = *reinterpret_cast<const float4 *>(orow + j + e);
+                ov[e] = a.x, ov[e + 1] = a.y, ov[e + 2] = a.z, ov[e + 3] = a.w;
+            }
+            unpack16<T>(ld_v4(grow + j), gz);
+#pragma unroll
+            for (int e = 0; e < V; ++e) ss = fmaf(ov[e], ov[e], ss);
+        }
+        ss = block_sum(ss, red);
+        const float inv = rsqrtf(ss / (float)vdim + eps);
+        if (j < vdim) {
+            float y[V];
+#pragma unroll
+            for (int e = 0; e < V; ++e) y[e] = ov[e] * inv * w[j + e] * (gz[e] / (1.0f + expf(-gz[e])));
+            st_v4(out_row + j, pack16<T>(y));
+        }
+        return;
+    }
     for (int j = threadIdx.x; j < vdim; j += blockDim.x) ss = fmaf(orow[j], orow[j], ss);
     ss = block_sum(ss, red);
     const float inv = rsqrtf(ss / (float)vdim + eps);
     for (int j = threadIdx.x; j < vdim; j += blockDim.x) {
-        const float z = Elem<T>::to_f(gate_in[(size_t)t * gate_ld + h * vdim + j]);
+        const float z = Elem<T>::to_f(grow[j]);
         const float y = orow[j] * inv * w[j] * (z / (1.0f + expf(-z)));
-        out[((size_t)t * heads + h) * vdim + j] = Elem<T>::from_f(y);
+        out_row[j] = Elem<T>::from_f(y);
     }
 }
 
@@ -441,7 +470,10 @@ int launch_gla_output(int dtype, const float *o, const float *w, float eps, cons
                       int heads, int vdim, cudaStream_t st) {
     if (tokens == 0) return B200_OK;
     B200_DISPATCH_DTYPE(dtype, {
-        gla_output_kernel<T><<<dim3(tokens, heads), 128, 0, st>>>(o, w, eps, (const T *)gate_in, gate_ld, (T *)out, heads, vdim);
+        constexpr int V = Elem<T>::kVec;
+        // rows that go in 16-byte pieces need one thread per piece; others keep 128 threads striding the row
+        const int threads = (vdim % V == 0 && vdim / V <= 128) ? std::max(32, (vdim / V + 31) / 32 * 32) : 128;
+        gla_output_kernel<T><<<dim3(tokens, heads), threads, 0, st>>>(o, w, eps, (const T *)gate_in, gate_ld, (T *)out, heads, vdim);
     });
     return cuda_status("gla_output launch");
 }

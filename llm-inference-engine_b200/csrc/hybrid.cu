@@ -41,24 +41,75 @@ __global__ void __launch_bounds__(256)
 postnorm_residual_kernel(float *__restrict__ x, const T *__restrict__ y_dense, const T *__restrict__ y_rows, const int *__restrict__ pair_row,
                          int top, const T *__restrict__ y_shared, const float *__restrict__ shared_gate, const float *__restrict__ g, float eps,
                          int width, float *__restrict__ trace, T *__restrict__ h_out) {
-    extern __shared__ float ys[];  // [width]
+    extern __shared__ __align__(16) float ys[];  // [width]
     __shared__ float red[33];
     const int t = blockIdx.x;
+    constexpr int V = Elem<T>::kVec;
+    // 16-byte pieces when every row starts on a 16-byte boundary (the sums are formed in the same order as element by element)
+    const bool vec = width % V == 0 && ((reinterpret_cast<size_t>(x) | reinterpret_cast<size_t>(y_dense) | reinterpret_cast<size_t>(y_rows) |
+                                         reinterpret_cast<size_t>(y_shared) | reinterpret_cast<size_t>(g) | reinterpret_cast<size_t>(trace) |
+                                         reinterpret_cast<size_t>(h_out)) & 15) == 0;
     float ss = 0.0f;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        float v;
-        if (y_dense) {
-            v = Elem<T>::to_f(y_dense[(size_t)t * width + c]);
-        } else {
-            v = 0.0f;
-            for (int k = 0; k < top; ++k) v += Elem<T>::to_f(y_rows[(size_t)pair_row[(size_t)t * top + k] * width + c]);
-            if (y_shared) v = fmaf(shared_gate[t], Elem<T>::to_f(y_shared[(size_t)t * width + c]), v);
+    if (vec) {
+        const float sg = (!y_dense && y_shared) ? shared_gate[t] : 0.0f;
+        for (int c = threadIdx.x * V; c < width; c += blockDim.x * V) {
+            float v[V];
+            if (y_dense) {
+                unpack16<T>(ld_v4(y_dense + (size_t)t * width + c), v);
+            } else {
+#pragma unroll
+                for (int i = 0; i < V; ++i) v[i] = 0.0f;
+                for (int k = 0; k < top; ++k) {
+                    float f[V];
+                    unpack16<T>(ld_v4(y_rows + (size_t)pair_row[(size_t)t * top + k] * width + c), f);
+#pragma unroll
+                    for (int i = 0; i < V; ++i) v[i] += f[i];
+                }
+                if (y_shared) {
+                    float f[V];
+                    unpack16<T>(ld_v4(y_shared + (size_t)t * width + c), f);
+#pragma unroll
+                    for (int i = 0; i < V; ++i) v[i] = fmaf(sg, f[i], v[i]);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < V; i += 4) *reinterpret_cast<float4 *>(ys + c + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+#pragma unroll
+            for (int i = 0; i < V; ++i) ss = fmaf(v[i], v[i], ss);
         }
-        ys[c] = v;
-        ss = fmaf(v, v, ss);
+    } else {
+        for (int c = threadIdx.x; c < width; c += blockDim.x) {
+            float v;
+            if (y_dense) {
+                v = Elem<T>::to_f(y_dense[(size_t)t * width + c]);
+            } else {
+                v = 0.0f;
+                for (int k = 0; k < top; ++k) v += Elem<T>::to_f(y_rows[(size_t)pair_row[(size_t)t * top + k] * width + c]);
+                if (y_shared) v = fmaf(shared_gate[t], Elem<T>::to_f(y_shared[(size_t)t * width + c]), v);
+            }
+            ys[c] = v;
+            ss = fmaf(v, v, ss);
+        }
     }
     ss = block_sum(ss, red);
     const float inv = rsqrtf(ss / (float)width + eps);
+    if (vec) {
+        for (int c = threadIdx.x * V; c < width; c += blockDim.x * V) {  // a thread reads back the pieces of ys it wrote
+            float v[V];
+#pragma unroll
+            for (int i = 0; i < V; i += 4) {
+                const float4 xv = *reinterpret_cast<const float4 *>(x + (size_t)t * width + c + i);
+                const float4 gv = *reinterpret_cast<const float4 *>(g + c + i);
+                const float4 yv = *reinterpret_cast<const float4 *>(ys + c + i);
+                const float4 r = make_float4(xv.x + yv.x * inv * gv.x, xv.y + yv.y * inv * gv.y, xv.z + yv.z * inv * gv.z, xv.w + yv.w * inv * gv.w);
+                *reinterpret_cast<float4 *>(x + (size_t)t * width + c + i) = r;
+                if (trace) *reinterpret_cast<float4 *>(trace + (size_t)t * width + c + i) = r;
+                v[i] = r.x, v[i + 1] = r.y, v[i + 2] = r.z, v[i + 3] = r.w;
+            }
+            if (h_out) st_v4(h_out + (size_t)t * width + c, pack16<T>(v));  // what the next sublayer's projections read (16-bit engines)
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
         const float v = x[(size_t)t * width + c] + ys[c] * inv * g[c];
         x[(size_t)t * width + c] = v;

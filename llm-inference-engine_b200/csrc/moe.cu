@@ -245,10 +245,21 @@ int launch_dense_f32out(int dtype, const void *x, const void *w, float *y, int M
     return cuda_status("dense_f32out launch");
 }
 
+// one 16-byte piece per thread; the last n % kVec elements (and everything, if x is not 16-byte aligned) one by one
 template <typename T>
-__global__ void activation_kernel(T *__restrict__ x, size_t n, int act) {
+__global__ void activation_kernel(T *__restrict__ x, size_t n, int act, size_t n_vec) {
+    constexpr int V = Elem<T>::kVec;
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) x[i] = Elem<T>::from_f(act_apply(Elem<T>::to_f(x[i]), act));
+    if (i < n_vec) {
+        float f[V];
+        unpack16<T>(ld_v4(x + i * V), f);
+#pragma unroll
+        for (int e = 0; e < V; ++e) f[e] = act_apply(f[e], act);
+        st_v4(x + i * V, pack16<T>(f));
+    } else {
+        const size_t j = n_vec * V + (i - n_vec);
+        if (j < n) x[j] = Elem<T>::from_f(act_apply(Elem<T>::to_f(x[j]), act));
+    }
 }
 
 int launch_moe_route_sigmoid(const float *logits, int ld, int *sel_expert, float *sel_weight, float *shared_gate, int tokens,
@@ -298,7 +309,11 @@ int launch_moe_grouped_gemm(int dtype, const void *a, const void *w, void *c, co
 
 int launch_activation(int dtype, void *x, size_t n, int act, cudaStream_t st) {
     if (n == 0) return B200_OK;
-    B200_DISPATCH_DTYPE(dtype, { activation_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, st>>>((T *)x, n, act); });
+    B200_DISPATCH_DTYPE(dtype, {
+        const size_t n_vec = (reinterpret_cast<size_t>(x) & 15) == 0 ? n / Elem<T>::kVec : 0;
+        const size_t threads = n_vec + (n - n_vec * Elem<T>::kVec);
+        activation_kernel<T><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>((T *)x, n, act, n_vec);
+    });
     return cuda_status("activation launch");
 }
 
