@@ -23,27 +23,67 @@ attn_qk_norm_cache_kernel(const T *__restrict__ proj, int ld, T *__restrict__ q_
     const int t = blockIdx.x;
     const int nq = heads * dim, nk = kv_heads * dim;
     const T *row = proj + (size_t)t * ld;
+    constexpr int V = Elem<T>::kVec;
+    // 16-byte pieces when rows, heads and the pools' rows all start on 16-byte boundaries
+    const bool vec = nq % V == 0 && dim % V == 0 && ld % V == 0 &&
+                     ((reinterpret_cast<size_t>(proj) | reinterpret_cast<size_t>(q_out) | reinterpret_cast<size_t>(k_pool) |
+                       reinterpret_cast<size_t>(v_pool) | reinterpret_cast<size_t>(q_norm) | reinterpret_cast<size_t>(k_norm)) & 15) == 0;
     float sq = 0.0f, sk = 0.0f;
-    for (int c = threadIdx.x; c < nq; c += blockDim.x) {
-        const float v = Elem<T>::to_f(row[c]);
-        sq = fmaf(v, v, sq);
-    }
-    for (int c = threadIdx.x; c < nk; c += blockDim.x) {
-        const float v = Elem<T>::to_f(row[nq + c]);
-        sk = fmaf(v, v, sk);
+    if (vec) {
+        for (int c = threadIdx.x * V; c < nq + nk; c += blockDim.x * V) {  // nq is a multiple of V: a piece is all q or all k
+            float f[V];
+            unpack16<T>(ld_v4(row + c), f);
+            float ss = 0.0f;
+#pragma unroll
+            for (int e = 0; e < V; ++e) ss = fmaf(f[e], f[e], ss);
+            if (c < nq) sq += ss; else sk += ss;
+        }
+    } else {
+        for (int c = threadIdx.x; c < nq; c += blockDim.x) {
+            const float v = Elem<T>::to_f(row[c]);
+            sq = fmaf(v, v, sq);
+        }
+        for (int c = threadIdx.x; c < nk; c += blockDim.x) {
+            const float v = Elem<T>::to_f(row[nq + c]);
+            sk = fmaf(v, v, sk);
+        }
     }
     sq = block_sum(sq, red);
     sk = block_sum(sk, red);
     const float iq = q_norm ? rsqrtf(sq / (float)nq + eps) : 1.0f;
     const float ik = k_norm ? rsqrtf(sk / (float)nk + eps) : 1.0f;
+    const int pos = tok_pos[t];
+    const int page = block_table[(size_t)tok_seq[t] * mpps + pos / kPage];
+    const int off = pos % kPage;
+    if (vec) {
+        for (int c = threadIdx.x * V; c < nq + nk; c += blockDim.x * V) {
+            const uint4 raw = ld_v4(row + c);
+            float f[V];
+            unpack16<T>(raw, f);
+            const bool is_q = c < nq;
+            const float *nw = is_q ? q_norm : k_norm;
+            if (nw) {
+                const float inv = is_q ? iq : ik;
+                const int cn = is_q ? c : c - nq;
+#pragma unroll
+                for (int e = 0; e < V; ++e) f[e] = f[e] * inv * nw[cn + e];
+            }
+            if (is_q) {
+                st_v4(q_out + (size_t)t * nq + c, nw ? pack16<T>(f) : raw);
+            } else if (page >= 0) {  // no page held: nothing is written (the host refuses such a batch)
+                const int ck = c - nq, g = ck / dim, cc = ck - g * dim;
+                const size_t at = (((size_t)page * kv_heads + g) * kPage + off) * dim + cc;
+                st_v4(k_pool + at, nw ? pack16<T>(f) : raw);
+                st_v4(v_pool + at, raw);
+            }
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < nq; c += blockDim.x) {
         const float v = Elem<T>::to_f(row[c]);
         q_out[(size_t)t * nq + c] = Elem<T>::from_f(q_norm ? v * iq * q_norm[c] : v);
     }
-    const int pos = tok_pos[t];
-    const int page = block_table[(size_t)tok_seq[t] * mpps + pos / kPage];
     if (page < 0) return;  // no page held: nothing is written (the host refuses such a batch)
-    const int off = pos % kPage;
     for (int c = threadIdx.x; c < nk; c += blockDim.x) {
         const int g = c / dim, cc = c - g * dim;
         const float v = Elem<T>::to_f(row[nq + c]);

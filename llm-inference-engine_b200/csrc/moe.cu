@@ -83,6 +83,23 @@ moe_gather_kernel(const float *__restrict__ x, const int *__restrict__ row_token
     if (r >= *n_tiles * tile) return;
     const int t = row_token[r];
     const float w = row_weight[r];
+    constexpr int V = Elem<T>::kVec;
+    if (width % V == 0 && ((reinterpret_cast<size_t>(x) | reinterpret_cast<size_t>(xg)) & 15) == 0) {  // 16-byte pieces of the output row
+        for (int c = threadIdx.x * V; c < width; c += blockDim.x * V) {
+            float f[V];
+#pragma unroll
+            for (int e = 0; e < V; e += 4) {
+                const float4 a = t >= 0 ? *reinterpret_cast<const float4 *>(x + (size_t)t * width + c + e) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                f[e] = w * a.x, f[e + 1] = w * a.y, f[e + 2] = w * a.z, f[e + 3] = w * a.w;
+            }
+            if (t < 0) {
+#pragma unroll
+                for (int e = 0; e < V; ++e) f[e] = 0.0f;  // padding rows are exact zeros whatever their weight slot holds
+            }
+            st_v4(xg + (size_t)r * width + c, pack16<T>(f));
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < width; c += blockDim.x)
         xg[(size_t)r * width + c] = Elem<T>::from_f(t >= 0 ? w * x[(size_t)t * width + c] : 0.0f);
 }
