@@ -6,7 +6,7 @@
 // The state of a sequence lives in a slot of a pool ([slots, heads, dim, vdim] fp32) between calls; a portion that starts at position 0
 // starts from zero.  Columns of S are independent of one another, so a head is cut into column tiles, one CTA each: the grid is
 // (vdim tiles, heads, sequences), the token loop is serial inside a CTA, the tile of S stays in shared memory for the whole portion.
-// Decoding is the same kernel with one token per sequence.
+// One-token portions (decoding) have a kernel of their own, laid out for one pass over the state (gla_step_kernel).
 #include "hybrid_ops.cuh"
 
 namespace b200 {
