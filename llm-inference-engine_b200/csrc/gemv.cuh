@@ -10,7 +10,7 @@
 //   * weight rows are contiguous in the [N,K] packing, so a unit (or an 8 KiB-per-row piece of it when rows are longer) is
 //     fetched with ONE 1-D TMA bulk copy per row (cp.async.bulk.shared.global, up to 8 KiB each) into a group-shared ring
 //     of stages with full/empty mbarriers: no registers are held by loads in flight and a single lane issues a whole
-//     stage (SASS: UBLKCP + SYNCS);
+//     stage;
 //   * the ring is filled BEFORE griddepcontrol.wait, so under programmatic dependent launch the weight stream of kernel i+1
 //     is already in flight while kernel i drains;
 //   * the activation rows live in shared memory (optionally produced by the fused add-residual + bias + RMSNorm prologue,

@@ -486,3 +486,23 @@ def test_sizes_that_fit_no_vector_or_tile(dtype, tol):
         want = want_logits(config, W, req[name])
         per_pos = np.linalg.norm(got[name] - want, axis=-1) / np.linalg.norm(want, axis=-1)
         assert np.median(per_pos) < tol and per_pos.max() < 5 * tol, (name, float(np.median(per_pos)), float(per_pos.max()))
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 5e-5), ("bfloat16", 4e-2)])
+def test_sizes_that_fit_every_vector(dtype, tol):
+    """The opposite corner: every row starts on a 16-byte boundary, so the 16-byte paths of the norm, gather, activation, output and
+    append kernels run; a chunk long enough for the per-token attention's widest block with decoded tokens on both sides of its edge;
+    a decay rank read in whole vectors; one-token portions on the recurrence's step kernel with a partial last column tile (vdim 72),
+    beside longer portions of another sequence in the same call.  Every expert is chosen (no close routing calls)."""
+    layers = [ref.gla_layer(heads=2, dim=24, vdim=72, tau=5.0, mlp=ref.moe(experts=4, top=4, ff=32, shared_ff=48)),
+              ref.attention_layer(heads=4, kv_heads=2, dim=32, size=520, scale=0.2, mlp=ref.moe(experts=3, top=3, ff=40, shared_ff=16)),
+              ref.gla_layer(heads=3, dim=40, vdim=16, tau=12.0)]
+    config = ref.make_config(layers, width=64)
+    W, packed = ref.make_weights(config, seed=91, decay_rank=16)
+    req = {"a": tokens_of(config, 530, 3), "b": tokens_of(config, 40, 4)}
+    schedule = [[("a", 500)]] + [[("a", 1)]] * 10 + [[("a", 1), ("b", 25)]] * 1 + [[("a", 1), ("b", 1)]] * 15 + [[("a", 4)]]
+    got = replay(session(config, packed, dtype=dtype, pool_tokens=704, max_batch_tokens=512), req, schedule)
+    for name in req:
+        want = want_logits(config, W, req[name])
+        per_pos = np.linalg.norm(got[name] - want, axis=-1) / np.linalg.norm(want, axis=-1)
+        assert np.median(per_pos) < tol and per_pos.max() < 5 * tol, (name, float(np.median(per_pos)), float(per_pos.max()))
