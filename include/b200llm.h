@@ -423,16 +423,27 @@ int b200_lm_head_topk_sample(b200_decoder_t *dec, const void *hidden, const void
  * (absent from the reference, whose only model is the Llama-2 decoder of src/models/llama/llama.cpp.)  A decoder whose layers are
  * described one by one: every layer has a token mixer of some kind (b200_mixer_kind_t) and, optionally, a feed-forward of some kind
  * (b200_mlp_kind_t); its sizes and constants are fields of the layer, so one engine serves any order and any sizes.  The residual stream
- * is fp32 and the norm sits on the sublayer OUTPUT:  x += rmsnorm(mixer(x)) * g1;  x += rmsnorm(ff(x)) * g2.
+ * is fp32; the norm sits on the sublayer OUTPUT (x += rmsnorm(mixer(x)) * g1;  x += rmsnorm(ff(x)) * g2) or on both sides of it
+ * (b200_norm_kind_t).
  * One forward call runs a RAGGED, MIXED batch: every sequence brings a portion of consecutive tokens (a whole prompt, a piece of one,
  * or a single decoded token) that continues from what earlier calls left in the paged key/value pool (attention layers) and in the
  * sequence's state slot (recurrent layers).  Prefill and decode are the same call. */
 typedef enum {
     B200_MIXER_ATTN_CHUNKED = 1, /* softmax attention, no rotation, block-diagonal causal mask, optional sink, sigmoid output gate      */
-    B200_MIXER_GLA = 2           /* gated linear attention: per-key-channel decay, fp32 matrix state per head                         */
+    B200_MIXER_GLA = 2,          /* gated linear attention: per-key-channel decay, fp32 matrix state per head                         */
+    B200_MIXER_LATENT = 3        /* latent attention: keys and values are up-projections of ONE cached low-rank row per position, plus
+                                    one rotated key part shared by the heads; sliding window, optional sink, sigmoid output gate      */
 } b200_mixer_kind_t;
-typedef enum { B200_MLP_NONE = 0, B200_MLP_MOE = 1 } b200_mlp_kind_t;
+typedef enum { B200_MLP_NONE = 0, B200_MLP_MOE = 1, B200_MLP_DENSE = 2 } b200_mlp_kind_t;
 typedef enum { B200_ACT_RELU2 = 0, B200_ACT_SILU = 1, B200_ACT_GELU_TANH = 2 } b200_act_t;
+typedef enum {
+    B200_NORM_RMS_POST = 0,      /* x += rmsnorm(sublayer(x)) * g                                                                     */
+    B200_NORM_DYT_PRE_POST = 1   /* x += ls * dyt_b(sublayer(dyt_a(x))), dyt(v) = tanh(alpha v) * w + b: no mean, no variance         */
+} b200_norm_kind_t;
+typedef enum {
+    B200_ROUTE_SIGMOID = 0,      /* scores = sigmoid(logits), the chosen scores are the weights, applied to the expert's INPUT        */
+    B200_ROUTE_SOFTMAX = 1       /* scores = softmax(logits); choice by score + bias; weights = chosen scores / their sum, on the OUTPUT */
+} b200_route_kind_t;
 
 typedef struct {
     int width, vocab, num_layers;
@@ -442,30 +453,55 @@ typedef struct {
     int max_tokens;     /* tokens of one forward call (sizes the scratch)                                                             */
     int max_seqs;       /* sequences of one forward call                                                                              */
     int max_pages_per_seq;
+    float embed_scale;  /* x = embedding[token] * embed_scale; 0 reads as 1                                                           */
+    float logit_softcap;/* logits <- cap * tanh(logits / cap); 0: none                                                                */
+    int final_norm;     /* b200_norm_kind_t of the model's last norm (RMS_POST: plain RMS norm; DYT: packed [w | b | alpha])          */
 } b200_hybrid_config_t;
 
 typedef struct {
     int mixer;          /* b200_mixer_kind_t                                                                                          */
     int heads, kv_heads, dim, vdim;
-    float scale;        /* ATTN: score scale                                                                                          */
+    float scale;        /* ATTN, LATENT: score scale                                                                                  */
     int chunk;          /* ATTN: position i sees j <= i with floor(i/chunk) == floor(j/chunk); 0 = plain causal                       */
     float tau;          /* GLA: decay = sigmoid(z)^(1/tau)                                                                            */
     int decay_rank;     /* GLA: inner size of the low-rank decay projection                                                           */
     int mlp;            /* b200_mlp_kind_t                                                                                            */
-    int experts, top, expert_ff, shared_ff; /* MOE; shared_ff == 0: no shared expert                                                  */
-    int act;            /* b200_act_t of the experts                                                                                  */
+    int experts, top, expert_ff, shared_ff; /* MOE; shared_ff == 0: no shared expert.  DENSE: expert_ff is the inner size             */
+    int act;            /* b200_act_t of the experts / the dense feed-forward                                                         */
     /* ---- weights: matrices [out, in] row-major of the engine dtype, vectors fp32 */
     const void *w_in;   /* ATTN: rows q (heads*dim), k (kv_heads*dim), gate (heads*dim);  GLA: rows q, k (heads*dim each), v, gate
-                           (heads*vdim each), decay-in (decay_rank).  K = width                                                       */
+                           (heads*vdim each), decay-in (decay_rank);  LATENT: rows q (heads*(dim+rot_dim), per head [dim | rot_dim]),
+                           gate (heads*vdim) and, unless kv_from >= 0, the down-projection (kv_rank + rot_dim).  K = width            */
     const void *w_out;  /* [width, heads*vdim]                                                                                        */
     const float *q_norm, *k_norm; /* ATTN: [heads*dim], [kv_heads*dim]: RMS norm over the WHOLE projection                            */
-    const float *sink;  /* ATTN: [heads] or NULL                                                                                      */
+    const float *sink;  /* ATTN, LATENT: [heads] or NULL                                                                              */
     const void *w_decay; const float *decay_bias; /* GLA: [heads*dim, decay_rank], [heads*dim]                                        */
     const float *out_norm;        /* GLA: [vdim], shared by the heads                                                                 */
-    const float *norm1, *norm2;   /* [width]                                                                                          */
-    const void *w_router;         /* MOE: [experts + 1, width]: router rows, then the shared expert's gate row (zeros if none)        */
-    const void *w_up, *w_down;    /* MOE: [experts, expert_ff, width], [experts, width, expert_ff]                                    */
-    const void *w_shared_up, *w_shared_down; /* [shared_ff, width], [width, shared_ff]                                                */
+    const float *norm1, *norm2;   /* RMS_POST: [width]                                                                                */
+    const void *w_router;         /* MOE: SIGMOID: [experts + 1, width]: router rows, then the shared expert's gate row (zeros if none);
+                                     SOFTMAX: [experts + identity, width]                                                            */
+    const void *w_up, *w_down;    /* MOE: [experts, expert_ff, width] ([experts, 2*expert_ff, width] when gated: gate rows, then up
+                                     rows), [experts, width, expert_ff];  DENSE: [expert_ff, width], [width, expert_ff]               */
+    const void *w_shared_up, *w_shared_down; /* [shared_ff, width] ([2*shared_ff, width] when gated), [width, shared_ff]              */
+    /* ---- fields of the later kinds (zero / NULL for the kinds above) */
+    int norm;           /* b200_norm_kind_t                                                                                           */
+    int window;         /* LATENT: position i sees j with 0 <= i - j < window; 0 = plain causal                                       */
+    int kv_rank;        /* LATENT: size of the cached latent row                                                                      */
+    int rot_dim;        /* LATENT: rotated query / key dimensions per head (the key's are shared by the heads and cached)             */
+    int rot_dims;       /* LATENT: how many of the rot_dim dimensions rotate (pairs i, i + rot_dims/2); the rest pass unchanged       */
+    float rot_base;     /* LATENT: angle of pair i at position p is p * rot_base^(-2i / rot_dims)                                     */
+    int kv_from;        /* LATENT: -1: this layer projects and caches its own latent rows; j >= 0: it reads layer j's                 */
+    int route;          /* MOE: b200_route_kind_t                                                                                     */
+    int identity;       /* MOE, SOFTMAX: router outputs past `experts` whose expert returns its input                                 */
+    int gated;          /* MOE, DENSE: 1: inner = act(gate rows . h) * (up rows . h)                                                  */
+    const float *kv_norm;         /* LATENT: [kv_rank]: RMS norm weight of the latent row                                             */
+    const void *w_uk_t;           /* LATENT: [heads, kv_rank, dim]: per head, the key up-projection TRANSPOSED (q is moved into the
+                                     latent space instead of the keys out of it)                                                      */
+    const void *w_uv;             /* LATENT: [heads, vdim, kv_rank]                                                                   */
+    const float *pre1, *post1, *pre2, *post2; /* DYT_PRE_POST: packed [w (width) | b (width) | alpha]                                 */
+    const float *ls1, *ls2;       /* DYT_PRE_POST: [width] layer scale, or NULL                                                       */
+    const float *route_bias;      /* MOE, SOFTMAX: [experts + identity] added to the scores for the choice only, or NULL              */
+    const float *b_up, *b_down;   /* DENSE: [expert_ff], [width], or NULL                                                             */
 } b200_hybrid_layer_t;
 
 typedef struct {
@@ -482,11 +518,12 @@ typedef struct b200_hybrid b200_hybrid_t;
 b200_hybrid_t *b200_hybrid_create(const b200_hybrid_config_t *cfg);
 void b200_hybrid_destroy(b200_hybrid_t *m);
 int b200_hybrid_set_layer(b200_hybrid_t *m, int layer, const b200_hybrid_layer_t *w);
-/* embedding [vocab, width], lm_head [vocab, width] (engine dtype), final_norm fp32 [width] */
+/* embedding [vocab, width], lm_head [vocab, width] (engine dtype), final_norm fp32 [width] (DYT: packed [w | b | alpha]) */
 int b200_hybrid_set_io(b200_hybrid_t *m, const void *embedding, const float *final_norm, const void *lm_head);
 size_t b200_hybrid_scratch_bytes(const b200_hybrid_t *m);
 int b200_hybrid_set_scratch(b200_hybrid_t *m, void *ptr, size_t bytes);
-/* Key/value pool: per attention layer K [num_pages, kv_heads, B200_KV_PAGE_SIZE, dim] then V, of the engine dtype (layers may differ in
+/* Key/value pool: per attention layer K [num_pages, kv_heads, B200_KV_PAGE_SIZE, dim] then V; per latent layer with a cache of its own
+ * [num_pages, B200_KV_PAGE_SIZE, kv_rank + rot_dim] (latent row, then the rotated key part), of the engine dtype (layers may differ in
  * size; each starts 256-byte aligned).  State pool: per recurrent layer fp32 [num_slots, heads, dim, vdim].  Caller-owned. */
 size_t b200_hybrid_kv_pool_bytes(const b200_hybrid_t *m, int num_pages);
 size_t b200_hybrid_state_pool_bytes(const b200_hybrid_t *m, int num_slots);

@@ -61,7 +61,8 @@ class BatchPlan(C.Structure):
 class HybridConfig(C.Structure):
     """b200_hybrid_config_t (include/b200llm.h)."""
     _fields_ = [("width", C.c_int), ("vocab", C.c_int), ("num_layers", C.c_int), ("dtype", C.c_int), ("norm_eps", C.c_float),
-                ("max_tokens", C.c_int), ("max_seqs", C.c_int), ("max_pages_per_seq", C.c_int)]
+                ("max_tokens", C.c_int), ("max_seqs", C.c_int), ("max_pages_per_seq", C.c_int), ("embed_scale", C.c_float),
+                ("logit_softcap", C.c_float), ("final_norm", C.c_int)]
 
 
 class HybridLayer(C.Structure):
@@ -72,7 +73,12 @@ class HybridLayer(C.Structure):
                 ("w_in", C.c_void_p), ("w_out", C.c_void_p), ("q_norm", C.c_void_p), ("k_norm", C.c_void_p), ("sink", C.c_void_p),
                 ("w_decay", C.c_void_p), ("decay_bias", C.c_void_p), ("out_norm", C.c_void_p), ("norm1", C.c_void_p), ("norm2", C.c_void_p),
                 ("w_router", C.c_void_p), ("w_up", C.c_void_p), ("w_down", C.c_void_p), ("w_shared_up", C.c_void_p),
-                ("w_shared_down", C.c_void_p)]
+                ("w_shared_down", C.c_void_p),
+                ("norm", C.c_int), ("window", C.c_int), ("kv_rank", C.c_int), ("rot_dim", C.c_int), ("rot_dims", C.c_int), ("rot_base", C.c_float),
+                ("kv_from", C.c_int), ("route", C.c_int), ("identity", C.c_int), ("gated", C.c_int),
+                ("kv_norm", C.c_void_p), ("w_uk_t", C.c_void_p), ("w_uv", C.c_void_p), ("pre1", C.c_void_p), ("post1", C.c_void_p),
+                ("pre2", C.c_void_p), ("post2", C.c_void_p), ("ls1", C.c_void_p), ("ls2", C.c_void_p), ("route_bias", C.c_void_p),
+                ("b_up", C.c_void_p), ("b_down", C.c_void_p)]
 
 
 class HybridBatch(C.Structure):
@@ -81,8 +87,10 @@ class HybridBatch(C.Structure):
                 ("seq_pos0", C.c_void_p), ("seq_slot", C.c_void_p), ("block_table", C.c_void_p), ("want_rows", C.c_void_p)]
 
 
-MIXER_ATTN_CHUNKED, MIXER_GLA = 1, 2
-MLP_NONE, MLP_MOE = 0, 1
+MIXER_ATTN_CHUNKED, MIXER_GLA, MIXER_LATENT = 1, 2, 3
+MLP_NONE, MLP_MOE, MLP_DENSE = 0, 1, 2
+NORM_RMS_POST, NORM_DYT_PRE_POST = 0, 1
+ROUTE_SIGMOID, ROUTE_SOFTMAX = 0, 1
 ACT_RELU2, ACT_SILU, ACT_GELU_TANH = 0, 1, 2
 (PLAN_MIXED_IDS, PLAN_MIXED_STARTS, PLAN_MIXED_POS0, PLAN_MIXED_SLOTS, PLAN_MIXED_REQUESTS, PLAN_MIXED_BLOCK_TABLE,
  PLAN_MIXED_SAMPLE_ROWS) = range(16, 23)

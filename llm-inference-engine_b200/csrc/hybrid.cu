@@ -1,11 +1,18 @@
 // hybrid.cu -- the layer-list decoder: a model given as a list of layers, each with a token mixer of some kind and an optional
 // feed-forward of some kind (b200_hybrid_layer_t), run over a ragged mixed batch of portions (b200_hybrid_batch_t).
 //
-// One layer = x += rmsnorm(mixer(x)) * g1;  x += rmsnorm(ff(x)) * g2, with x the fp32 residual stream.  Launch sequence per layer:
+// One layer = x += rmsnorm(mixer(x)) * g1;  x += rmsnorm(ff(x)) * g2 (B200_NORM_RMS_POST), or x += ls1 * dyt(mixer(dyt(x))); x += ls2 *
+// dyt(ff(dyt(x))) (B200_NORM_DYT_PRE_POST: the kernel that adds a sublayer's result also writes the next sublayer's normed input), with x
+// the fp32 residual stream.  Launch sequence per layer:
 //   fused input projection (b200_linear: tcgen05 GEMM / weight-streaming GEMV by token count)
 //   attention mixer:  q/k whole-projection norm + pool append -> chunked sink attention (gate fused) -> output projection
 //   gla mixer:        decay (low-rank, fp32) -> recurrence over the state slots -> head norm * silu(gate) -> output projection
+//   latent mixer:     split + rotation + latent-row norm + pool append -> grouped GEMM over the heads (q into the latent space) -> windowed
+//                     sink attention over the latent rows -> grouped GEMM over the heads (value up-projection) -> gate -> output projection
 //   post-norm + residual add (fp32)
+//   dense ff:         b200_linear up -> bias + act -> b200_linear down (its bias joins the residual kernel)
+//   moe (softmax):    router (fp32) -> route -> plan -> gather rows -> grouped gate|up -> act(gate) * up -> grouped down; shared expert alike;
+//                     combine (weights on the outputs, identity experts return the input) + norm + residual add, one kernel
 //   moe:              router + shared gate (fp32) -> route -> plan -> gather (weight on the input) -> grouped up (+act) -> grouped down
 //                     shared expert: b200_linear up -> act -> b200_linear down
 //                     combine (sum of the token's expert rows + gate * shared) + post-norm + residual add, one kernel
@@ -13,6 +20,7 @@
 // Everything is stream-ordered and allocation-free; the only host->device traffic of a call is one copy of the batch description.
 #include "hybrid_ops.cuh"
 
+#include <algorithm>
 #include <new>
 #include <vector>
 
@@ -23,14 +31,14 @@ static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
 template <typename T>
 __global__ void embed_f32_kernel(const int *__restrict__ ids, const T *__restrict__ table, float *__restrict__ x, T *__restrict__ h, int width,
-                                 int vocab) {
+                                 int vocab, float scale) {
     const int t = blockIdx.x;
     int id = ids[t];
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // the host has refused ids outside the vocabulary
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        const T v = table[(size_t)id * width + c];
-        x[(size_t)t * width + c] = Elem<T>::to_f(v);
-        if (h) h[(size_t)t * width + c] = v;  // the 16-bit copy the first projection reads
+        const float v = Elem<T>::to_f(table[(size_t)id * width + c]) * scale;
+        x[(size_t)t * width + c] = v;
+        if (h) h[(size_t)t * width + c] = Elem<T>::from_f(v);  // the 16-bit copy the first projection reads
     }
 }
 
@@ -116,6 +124,84 @@ postnorm_residual_kernel(float *__restrict__ x, const T *__restrict__ y_dense, c
         if (trace) trace[(size_t)t * width + c] = v;
         if (h_out) h_out[(size_t)t * width + c] = Elem<T>::from_f(v);  // what the next sublayer's projections read (16-bit engines)
     }
+}
+
+// packed Dynamic-Tanh parameters: [w (width) | b (width) | alpha]
+__device__ __forceinline__ float dyt_apply(const float *__restrict__ p, int width, int c, float alpha, float v) {
+    return fmaf(tanhf(alpha * v), p[c], p[width + c]);
+}
+
+// The general form of the kernel above, for either norm kind and either place of the routing weights:
+//   y[t, :]  = y_dense[t, :] + y_bias                                                  (a dense sublayer), or
+//            = sum_k w(t, k) * (pair_row[t, k] >= 0 ? y_rows[pair_row[t, k], :] : h_in[t, :]) + shared_gate[t] * y_shared[t, :]
+//              with w = pair_weight (NULL: 1) and shared_gate NULL: 1; a pair without a row is an identity expert;
+//   x[t, :] += ls * norm(y[t, :])    norm = RMS (post = g) or Dynamic Tanh (post packed);   has_y == 0: x stays as it is;
+//   h_out[t, :] = T(pre ? dyt(x[t, :]; pre) : x[t, :]): what the next sublayer's projections read.
+// h_in and h_out may be the same buffer: an element is read by the thread that overwrites it, before it does.
+template <typename T>
+__global__ void __launch_bounds__(256)
+sublayer_residual_kernel(float *__restrict__ x, const T *__restrict__ y_dense, const float *__restrict__ y_bias, const T *__restrict__ y_rows,
+                         const int *__restrict__ pair_row, const float *__restrict__ pair_weight, int top, const T *__restrict__ y_shared,
+                         const float *__restrict__ shared_gate, const T *h_in, int norm, const float *__restrict__ post,
+                         const float *__restrict__ ls, float eps, const float *__restrict__ pre, int width, float *__restrict__ trace, T *h_out,
+                         int has_y) {
+    extern __shared__ __align__(16) float ys[];  // [width]
+    __shared__ float red[33];
+    const int t = blockIdx.x;
+    float inv = 1.0f;
+    if (has_y) {
+        float ss = 0.0f;
+        for (int c = threadIdx.x; c < width; c += blockDim.x) {
+            float v;
+            if (y_dense) {
+                v = Elem<T>::to_f(y_dense[(size_t)t * width + c]) + (y_bias ? y_bias[c] : 0.0f);
+            } else {
+                v = 0.0f;
+                for (int k = 0; k < top; ++k) {
+                    const int r = pair_row[(size_t)t * top + k];
+                    const float w = pair_weight ? pair_weight[(size_t)t * top + k] : 1.0f;
+                    v = fmaf(w, Elem<T>::to_f(r >= 0 ? y_rows[(size_t)r * width + c] : h_in[(size_t)t * width + c]), v);
+                }
+                if (y_shared) v = fmaf(shared_gate ? shared_gate[t] : 1.0f, Elem<T>::to_f(y_shared[(size_t)t * width + c]), v);
+            }
+            ys[c] = v;
+            ss = fmaf(v, v, ss);
+        }
+        if (norm == B200_NORM_RMS_POST) {
+            ss = block_sum(ss, red);
+            inv = rsqrtf(ss / (float)width + eps);
+        }
+    }
+    const float a_post = (has_y && norm == B200_NORM_DYT_PRE_POST) ? post[2 * width] : 0.0f, a_pre = pre ? pre[2 * width] : 0.0f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {  // a thread reads back the elements of ys it wrote
+        float v = x[(size_t)t * width + c];
+        if (has_y) {
+            float n = norm == B200_NORM_RMS_POST ? ys[c] * inv * post[c] : dyt_apply(post, width, c, a_post, ys[c]);
+            if (ls) n *= ls[c];
+            v += n;
+            x[(size_t)t * width + c] = v;
+        }
+        if (trace) trace[(size_t)t * width + c] = v;
+        if (h_out) h_out[(size_t)t * width + c] = Elem<T>::from_f(pre ? dyt_apply(pre, width, c, a_pre, v) : v);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+final_dyt_rows_kernel(const float *__restrict__ x, const int *__restrict__ rows, const float *__restrict__ p, float *__restrict__ out,
+                      T *__restrict__ out_t, int width) {
+    const int i = blockIdx.x;
+    const float *xr = x + (size_t)rows[i] * width;
+    const float alpha = p[2 * width];
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float v = dyt_apply(p, width, c, alpha, xr[c]);
+        out[(size_t)i * width + c] = v;
+        if (out_t) out_t[(size_t)i * width + c] = Elem<T>::from_f(v);
+    }
+}
+
+__global__ void softcap_kernel(float *__restrict__ logits, size_t n, float cap) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) logits[i] = cap * tanhf(logits[i] / cap);
 }
 
 template <typename T>
@@ -233,7 +319,7 @@ int launch_proj_f32(int x_dtype, const void *x, int ldx, int w_dtype, const void
 
 struct LayerPlan {
     int n_in = 0;                     // rows of the fused input projection
-    size_t k_off = 0, v_off = 0;      // ATTN: byte offsets into the kv pool (set by set_pools)
+    size_t k_off = 0, v_off = 0;      // ATTN: byte offsets into the kv pool (set by set_pools); LATENT: k_off of the rows this layer reads
     size_t state_off = 0;             // GLA: byte offset into the state pool
 };
 
@@ -254,7 +340,7 @@ struct b200_hybrid {
     char *scratch = nullptr;
     float *x = nullptr, *f32a = nullptr, *f32b = nullptr, *xn = nullptr;
     void *h = nullptr, *proj = nullptr, *mix = nullptr, *mix2 = nullptr, *y = nullptr, *xg = nullptr, *u = nullptr, *yrows = nullptr, *us = nullptr,
-         *ys = nullptr;
+         *ys = nullptr, *lqn = nullptr, *lqr = nullptr, *lql = nullptr, *lol = nullptr, *lov = nullptr;
     int *meta = nullptr, *moe_i = nullptr;
     float *moe_f = nullptr;
     std::vector<int> host_meta;
@@ -263,7 +349,7 @@ struct b200_hybrid {
 namespace {
 
 struct Carve {
-    size_t x, f32a, f32b, xn, h, proj, mix, y, xg, u, yrows, us, ys, meta, moe_i, moe_f, total;
+    size_t x, f32a, f32b, xn, h, proj, mix, y, xg, u, yrows, us, ys, lqn, lqr, lql, lov, meta, moe_i, moe_f, total;
 };
 
 int max_rows_of(const b200_hybrid_config_t &c, const b200_hybrid_layer_t &l) {
@@ -273,24 +359,35 @@ int max_rows_of(const b200_hybrid_config_t &c, const b200_hybrid_layer_t &l) {
 
 int n_in_of(const b200_hybrid_layer_t &l) {
     if (l.mixer == B200_MIXER_ATTN_CHUNKED) return (2 * l.heads + l.kv_heads) * l.dim;
+    if (l.mixer == B200_MIXER_LATENT) return l.heads * (l.dim + l.rot_dim) + l.heads * l.vdim + (l.kv_from < 0 ? l.kv_rank + l.rot_dim : 0);
     return 2 * l.heads * l.dim + 2 * l.heads * l.vdim + l.decay_rank;
 }
 
 Carve carve(const b200_hybrid *m) {
     const b200_hybrid_config_t &c = m->cfg;
     const size_t T = (size_t)c.max_tokens, es = c.dtype == B200_F32 ? 4 : 2;
-    size_t n_in = 1, n_mix = 1, n_f32 = 1, rows = 0, ff = 1, sff = 1, experts = 1, top = 1;
+    size_t n_in = 1, n_mix = 1, n_f32 = 1, rows = 0, ff = 1, sff = 1, experts = 1, top = 1, lqn = 0, lqr = 0, lql = 0, lov = 0, lheads = 0;
+    const size_t t_pad = (T + 127) / 128 * 128;  // rows per head of the latent mixer's grouped GEMMs
     for (int i = 0; i < c.num_layers; ++i) {
         if (!m->layer_set[i]) continue;
         const b200_hybrid_layer_t &l = m->layers[i];
         n_in = std::max(n_in, (size_t)n_in_of(l));
         n_mix = std::max(n_mix, (size_t)l.heads * std::max(l.dim, l.vdim));
         n_f32 = std::max(n_f32, (size_t)l.heads * std::max(l.dim, l.vdim));
+        n_mix = std::max(n_mix, (size_t)l.heads * l.vdim);
+        if (l.mixer == B200_MIXER_LATENT) {
+            lqn = std::max(lqn, (size_t)l.heads * t_pad * l.dim), lqr = std::max(lqr, T * l.heads * l.rot_dim);
+            lql = std::max(lql, (size_t)l.heads * t_pad * l.kv_rank), lov = std::max(lov, (size_t)l.heads * t_pad * l.vdim);
+            lheads = std::max(lheads, (size_t)l.heads);
+        }
+        const size_t g = l.gated ? 3 : 1;  // gated: [gate | up] and the product beside it
         if (l.mlp == B200_MLP_MOE) {
             rows = std::max(rows, (size_t)max_rows_of(c, l));
-            ff = std::max(ff, (size_t)l.expert_ff), sff = std::max(sff, (size_t)l.shared_ff);
+            ff = std::max(ff, g * l.expert_ff), sff = std::max(sff, g * l.shared_ff);
             experts = std::max(experts, (size_t)l.experts), top = std::max(top, (size_t)l.top);
-            n_f32 = std::max(n_f32, (size_t)l.experts + 1);
+            n_f32 = std::max(n_f32, (size_t)l.experts + std::max(1, l.identity));
+        } else if (l.mlp == B200_MLP_DENSE) {
+            sff = std::max(sff, g * l.expert_ff);
         }
     }
     Carve k;
@@ -307,14 +404,18 @@ Carve carve(const b200_hybrid *m) {
     k.yrows = align256(rows * c.width * es);
     k.us = align256(T * sff * es);
     k.ys = align256(T * c.width * es);
+    k.lqn = align256(lqn * es), k.lqr = align256(lqr * es), k.lql = align256(lql * es), k.lov = align256(lov * es);
     // meta: attention tiles [4 * (T/64 + S), padded] | ids | tok_seq | tok_pos | want | short-portion token list [T each] | seq_start [S+1] |
     //       pos0 | slot [S each] | block table [S * mpps]
-    k.meta = align256((4 * (T / 64 + (size_t)c.max_seqs + 1) + 5 * T + 3 * (size_t)c.max_seqs + 1 + (size_t)c.max_seqs * c.max_pages_per_seq) * 4);
+    //       | latent mixers: head of every row tile [heads * t_pad / 64] | live row tiles per layer [layers]
+    k.meta = align256((4 * (T / 64 + (size_t)c.max_seqs + 1) + 5 * T + 3 * (size_t)c.max_seqs + 1 + (size_t)c.max_seqs * c.max_pages_per_seq +
+                       lheads * (t_pad / 64) + (size_t)c.num_layers) * 4);
     // moe ints: sel_expert | pair_row [T*top each] | row_token [rows] | tile_expert [rows / tile] | n_tiles
     k.moe_i = align256((2 * T * top + rows + rows / kMoeTileM + 4) * 4);
     // moe floats: sel_weight [T*top] | row_weight [rows] | shared_gate [T]
     k.moe_f = align256((T * top + rows + T) * 4);
-    k.total = k.x + k.f32a + k.f32b + k.xn + k.h + k.proj + 2 * k.mix + k.y + k.xg + k.u + k.yrows + k.us + k.ys + k.meta + k.moe_i + k.moe_f;
+    k.total = k.x + k.f32a + k.f32b + k.xn + k.h + k.proj + 2 * k.mix + k.y + k.xg + k.u + k.yrows + k.us + k.ys + k.lqn + k.lqr + 2 * k.lql +
+              k.lov + k.meta + k.moe_i + k.moe_f;
     return k;
 }
 
@@ -346,22 +447,44 @@ void b200_hybrid_destroy(b200_hybrid_t *m) { delete m; }
 int b200_hybrid_set_layer(b200_hybrid_t *m, int layer, const b200_hybrid_layer_t *w) {
     B200_REQUIRE(m && w, "hybrid_set_layer: null argument");
     B200_REQUIRE(layer >= 0 && layer < m->cfg.num_layers, "hybrid_set_layer: layer %d outside [0, %d)", layer, m->cfg.num_layers);
-    B200_REQUIRE(w->mixer == B200_MIXER_ATTN_CHUNKED || w->mixer == B200_MIXER_GLA, "hybrid_set_layer: unknown mixer kind %d", w->mixer);
-    B200_REQUIRE(w->heads > 0 && w->dim > 0 && w->w_in && w->w_out && w->norm1, "hybrid_set_layer: mixer sizes / weights missing");
+    B200_REQUIRE(w->mixer == B200_MIXER_ATTN_CHUNKED || w->mixer == B200_MIXER_GLA || w->mixer == B200_MIXER_LATENT,
+                 "hybrid_set_layer: unknown mixer kind %d", w->mixer);
+    B200_REQUIRE(w->norm == B200_NORM_RMS_POST || w->norm == B200_NORM_DYT_PRE_POST, "hybrid_set_layer: unknown norm kind %d", w->norm);
+    B200_REQUIRE(w->heads > 0 && w->dim > 0 && w->w_in && w->w_out, "hybrid_set_layer: mixer sizes / weights missing");
+    if (w->norm == B200_NORM_RMS_POST) B200_REQUIRE(w->norm1, "hybrid_set_layer: norm weight missing");
+    else B200_REQUIRE(w->pre1 && w->post1, "hybrid_set_layer: norm parameters missing");
     if (w->mixer == B200_MIXER_ATTN_CHUNKED) {
         B200_REQUIRE(w->kv_heads > 0 && w->heads % w->kv_heads == 0, "hybrid_set_layer: heads %d not a multiple of kv_heads %d", w->heads, w->kv_heads);
         B200_REQUIRE(w->vdim == w->dim, "hybrid_set_layer: this attention's values are its keys: vdim %d must equal dim %d", w->vdim, w->dim);
         B200_REQUIRE(w->chunk >= 0, "hybrid_set_layer: negative chunk");
+    } else if (w->mixer == B200_MIXER_LATENT) {
+        B200_REQUIRE(w->vdim > 0 && w->kv_rank > 0 && w->rot_dim >= 0 && w->window >= 0, "hybrid_set_layer: latent attention sizes missing");
+        B200_REQUIRE(w->rot_dims >= 0 && w->rot_dims <= w->rot_dim && w->rot_dims % 2 == 0 && (w->rot_dims == 0 || w->rot_base > 0.0f),
+                     "hybrid_set_layer: %d rotating dimensions do not fit a rotated part of %d (even, with a positive base)", w->rot_dims, w->rot_dim);
+        B200_REQUIRE(w->w_uk_t && w->w_uv, "hybrid_set_layer: latent attention up-projections missing");
+        B200_REQUIRE(w->kv_from < layer, "hybrid_set_layer: layer %d cannot read the latent rows of layer %d", layer, w->kv_from);
+        B200_REQUIRE(w->kv_from >= 0 || w->kv_norm, "hybrid_set_layer: latent row norm weight missing");
     } else {
         B200_REQUIRE(w->vdim > 0 && w->decay_rank > 0 && w->tau > 0.0f && w->w_decay && w->out_norm, "hybrid_set_layer: gla sizes / weights missing");
     }
-    B200_REQUIRE(w->mlp == B200_MLP_NONE || w->mlp == B200_MLP_MOE, "hybrid_set_layer: unknown feed-forward kind %d", w->mlp);
-    if (w->mlp == B200_MLP_MOE) {
-        B200_REQUIRE(w->experts > 0 && w->top > 0 && w->top <= w->experts && w->expert_ff > 0 && w->shared_ff >= 0,
-                     "hybrid_set_layer: bad expert counts");
-        B200_REQUIRE(w->w_router && w->w_up && w->w_down && w->norm2, "hybrid_set_layer: expert weights missing");
-        B200_REQUIRE(w->shared_ff == 0 || (w->w_shared_up && w->w_shared_down), "hybrid_set_layer: shared expert weights missing");
+    B200_REQUIRE(w->mlp == B200_MLP_NONE || w->mlp == B200_MLP_MOE || w->mlp == B200_MLP_DENSE, "hybrid_set_layer: unknown feed-forward kind %d", w->mlp);
+    if (w->mlp != B200_MLP_NONE) {
+        if (w->norm == B200_NORM_RMS_POST) B200_REQUIRE(w->norm2, "hybrid_set_layer: feed-forward norm weight missing");
+        else B200_REQUIRE(w->pre2 && w->post2, "hybrid_set_layer: feed-forward norm parameters missing");
         B200_REQUIRE(w->act >= B200_ACT_RELU2 && w->act <= B200_ACT_GELU_TANH, "hybrid_set_layer: unknown activation %d", w->act);
+        B200_REQUIRE(w->expert_ff > 0 && w->w_up && w->w_down, "hybrid_set_layer: feed-forward sizes / weights missing");
+    }
+    if (w->mlp == B200_MLP_MOE) {
+        B200_REQUIRE(w->experts > 0 && w->top > 0 && w->shared_ff >= 0 && w->identity >= 0, "hybrid_set_layer: bad expert counts");
+        B200_REQUIRE(w->route == B200_ROUTE_SIGMOID || w->route == B200_ROUTE_SOFTMAX, "hybrid_set_layer: unknown router kind %d", w->route);
+        if (w->route == B200_ROUTE_SIGMOID) {
+            B200_REQUIRE(w->top <= w->experts && w->identity == 0 && !w->gated, "hybrid_set_layer: the sigmoid router has no identity or gated experts");
+            B200_REQUIRE(w->norm == B200_NORM_RMS_POST, "hybrid_set_layer: the sigmoid router weighs the fp32 residual row: post-norm layers only");
+        } else {
+            B200_REQUIRE(w->top <= w->experts + w->identity, "hybrid_set_layer: top %d of %d router outputs", w->top, w->experts + w->identity);
+        }
+        B200_REQUIRE(w->w_router, "hybrid_set_layer: router weights missing");
+        B200_REQUIRE(w->shared_ff == 0 || (w->w_shared_up && w->w_shared_down), "hybrid_set_layer: shared expert weights missing");
     }
     m->layers[layer] = *w;
     m->layer_set[layer] = 1;
@@ -400,6 +523,11 @@ int b200_hybrid_set_scratch(b200_hybrid_t *m, void *ptr, size_t bytes) {
     m->yrows = p, p += k.yrows;
     m->us = p, p += k.us;
     m->ys = p, p += k.ys;
+    m->lqn = p, p += k.lqn;
+    m->lqr = p, p += k.lqr;
+    m->lql = p, p += k.lql;
+    m->lol = p, p += k.lql;
+    m->lov = p, p += k.lov;
     m->meta = (int *)p, p += k.meta;
     m->moe_i = (int *)p, p += k.moe_i;
     m->moe_f = (float *)p, p += k.moe_f;
@@ -411,8 +539,11 @@ size_t b200_hybrid_kv_pool_bytes(const b200_hybrid_t *m, int num_pages) {
     const size_t es = m->cfg.dtype == B200_F32 ? 4 : 2;
     size_t total = 0;
     for (int i = 0; i < m->cfg.num_layers; ++i)
-        if (m->layer_set[i] && m->layers[i].mixer == B200_MIXER_ATTN_CHUNKED)
+        if (!m->layer_set[i]) continue;
+        else if (m->layers[i].mixer == B200_MIXER_ATTN_CHUNKED)
             total += 2 * align256((size_t)num_pages * m->layers[i].kv_heads * kPageH * m->layers[i].dim * es);
+        else if (m->layers[i].mixer == B200_MIXER_LATENT && m->layers[i].kv_from < 0)
+            total += align256((size_t)num_pages * kPageH * (m->layers[i].kv_rank + m->layers[i].rot_dim) * es);
     return total ? total : 256;
 }
 
@@ -436,6 +567,16 @@ int b200_hybrid_set_pools(b200_hybrid_t *m, void *kv_pool, int num_pages, void *
         if (l.mixer == B200_MIXER_ATTN_CHUNKED) {
             const size_t one = align256((size_t)num_pages * l.kv_heads * kPageH * l.dim * es);
             m->plan[i].k_off = kv, m->plan[i].v_off = kv + one, kv += 2 * one;
+        } else if (l.mixer == B200_MIXER_LATENT) {
+            if (l.kv_from < 0) {
+                m->plan[i].k_off = kv, kv += align256((size_t)num_pages * kPageH * (l.kv_rank + l.rot_dim) * es);
+            } else {  // the rows of an earlier layer, which must own them and rotate them alike
+                const b200_hybrid_layer_t &o = m->layers[l.kv_from];
+                B200_REQUIRE(o.mixer == B200_MIXER_LATENT && o.kv_from < 0 && o.kv_rank == l.kv_rank && o.rot_dim == l.rot_dim &&
+                                 o.rot_dims == l.rot_dims && o.rot_base == l.rot_base,
+                             "hybrid_set_pools: layer %d cannot read the latent rows of layer %d (no cache of its own, or other sizes)", i, l.kv_from);
+                m->plan[i].k_off = m->plan[l.kv_from].k_off;
+            }
         } else {
             m->plan[i].state_off = stt, stt += align256((size_t)num_slots * l.heads * l.dim * l.vdim * 4);
         }
@@ -462,9 +603,17 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
     // ---- batch description: checked on the host, shipped in one copy
     std::vector<int> &hm = m->host_meta;
     const size_t n_tile_ints = 4 * ((size_t)NT / 64 + S + 1);
-    hm.assign(n_tile_ints + (size_t)5 * NT + 3 * S + 1 + (size_t)S * mpps, 0);
+    // latent mixers: their per-head products are grouped GEMMs over [heads, t_pad, *] with row tiles of 64; tile i belongs to head i / tph
+    const int t_pad = (NT + kMoeTileM - 1) / kMoeTileM * kMoeTileM, tph = t_pad / kMoeTileM;
+    int lat_heads = 0;
+    for (int i = 0; i < c.num_layers; ++i)
+        if (m->layers[i].mixer == B200_MIXER_LATENT) lat_heads = std::max(lat_heads, m->layers[i].heads);
+    hm.assign(n_tile_ints + (size_t)5 * NT + 3 * S + 1 + (size_t)S * mpps + (size_t)lat_heads * tph + c.num_layers, 0);
     int *h_tiles = hm.data(), *h_ids = h_tiles + n_tile_ints, *h_seq = h_ids + NT, *h_pos = h_seq + NT, *h_want = h_pos + NT, *h_short = h_want + NT,
-        *h_start = h_short + NT, *h_pos0 = h_start + S + 1, *h_slot = h_pos0 + S, *h_bt = h_slot + S;
+        *h_start = h_short + NT, *h_pos0 = h_start + S + 1, *h_slot = h_pos0 + S, *h_bt = h_slot + S, *h_lat_head = h_bt + (size_t)S * mpps,
+        *h_lat_n = h_lat_head + (size_t)lat_heads * tph;
+    for (int i = 0; i < lat_heads * tph; ++i) h_lat_head[i] = i / tph;
+    for (int i = 0; i < c.num_layers; ++i) h_lat_n[i] = m->layers[i].mixer == B200_MIXER_LATENT ? m->layers[i].heads * tph : 0;
     // prompt portions go to the tensor-core attention in tiles of <= 64 consecutive tokens, short ones (decoded tokens) to the per-token kernel
     constexpr int kShortPortion = 8;
     int n_tiles = 0, n_short = 0, gla_kinds = 0;
@@ -505,7 +654,8 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
     NvtxRange range("hybrid_forward");
     if (cudaMemcpyAsync(m->meta, hm.data(), hm.size() * sizeof(int), cudaMemcpyHostToDevice, st) != cudaSuccess) return cuda_status("hybrid_forward meta copy");
     const int *d_tiles = m->meta, *d_ids = d_tiles + n_tile_ints, *d_seq = d_ids + NT, *d_pos = d_seq + NT, *d_want = d_pos + NT, *d_short = d_want + NT,
-              *d_start = d_short + NT, *d_pos0 = d_start + S + 1, *d_slot = d_pos0 + S, *d_bt = d_slot + S;
+              *d_start = d_short + NT, *d_pos0 = d_start + S + 1, *d_slot = d_pos0 + S, *d_bt = d_slot + S, *d_lat_head = d_bt + (size_t)S * mpps,
+              *d_lat_n = d_lat_head + (size_t)lat_heads * tph;
 
     const int dt = c.dtype, width = c.width;
     const bool f32 = dt == B200_F32;
@@ -516,7 +666,8 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
         if (rc != B200_OK) return rc; \
     } while (0)
     // 16-bit engines: every kernel that writes the residual stream also writes its 16-bit copy h, which the next projections read
-    B200_DISPATCH_DTYPE(dt, { embed_f32_kernel<T><<<NT, 128, 0, st>>>(d_ids, (const T *)m->embedding, m->x, f32 ? nullptr : (T *)m->h, width, c.vocab); });
+    B200_DISPATCH_DTYPE(dt, { embed_f32_kernel<T><<<NT, 128, 0, st>>>(d_ids, (const T *)m->embedding, m->x, f32 ? nullptr : (T *)m->h, width, c.vocab,
+                                                                      c.embed_scale != 0.0f ? c.embed_scale : 1.0f); });
     auto cast_x = [&]() -> const void * { return f32 ? (const void *)m->x : (const void *)m->h; };
     auto postnorm = [&](const void *y_dense, const void *y_rows, const int *pair_row, int top, const void *y_shared, const float *gate,
                         const float *g, float *trace) -> int {
@@ -528,15 +679,37 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
         return cuda_status("postnorm_residual launch");
     };
 
+    // the general residual kernel: either norm kind, routing weights on the outputs, identity experts, the next sublayer's pre-norm fused
+    auto residual = [&](bool has_y, const void *y_dense, const float *y_bias, const void *y_rows, const int *pair_row, const float *pair_weight, int top,
+                        const void *y_shared, const float *gate, int norm, const float *post, const float *ls, const float *pre, float *trace) -> int {
+        B200_DISPATCH_DTYPE(dt, {
+            sublayer_residual_kernel<T><<<NT, 256, (size_t)width * sizeof(float), st>>>(
+                m->x, (const T *)y_dense, y_bias, (const T *)y_rows, pair_row, pair_weight, top, (const T *)y_shared, gate, (const T *)m->h, norm, post, ls,
+                c.norm_eps, pre, width, trace, (pre || !f32) ? (T *)m->h : nullptr, has_y ? 1 : 0);
+        });
+        return cuda_status("sublayer_residual launch");
+    };
+    // the pre-norm of the sublayer that follows sublayer `sub` (0: mixer, 1: feed-forward) of layer li, or NULL
+    auto next_pre = [&](int li, int sub) -> const float * {
+        const b200_hybrid_layer_t &l = m->layers[li];
+        if (sub == 0 && l.mlp != B200_MLP_NONE) return l.norm == B200_NORM_DYT_PRE_POST ? l.pre2 : nullptr;
+        if (li + 1 >= c.num_layers) return nullptr;
+        return m->layers[li + 1].norm == B200_NORM_DYT_PRE_POST ? m->layers[li + 1].pre1 : nullptr;
+    };
+    const size_t es = f32 ? 4 : 2;
+    bool h_normed = false;  // m->h holds the pre-normed input of the coming sublayer
+
     for (int li = 0; li < c.num_layers; ++li) {
         const b200_hybrid_layer_t &l = m->layers[li];
         const LayerPlan &lp = m->plan[li];
+        const bool dyt = l.norm == B200_NORM_DYT_PRE_POST;
         float *trace = (layer_trace && l.mlp == B200_MLP_NONE) ? layer_trace + (size_t)li * NT * width : nullptr;
-        const void *h = cast_x();
+        if (dyt && !h_normed) RUN(residual(false, nullptr, nullptr, nullptr, nullptr, nullptr, 0, nullptr, nullptr, l.norm, nullptr, nullptr, l.pre1, nullptr));
+        const void *h = dyt ? (const void *)m->h : cast_x();
         RUN(linear(m, h, l.w_in, m->proj, NT, width, lp.n_in, st));
+        int n_mixed = 0;  // columns of the mixer's result before the output projection
         if (l.mixer == B200_MIXER_ATTN_CHUNKED) {
             const int hd = l.heads * l.dim;
-            const size_t es = f32 ? 4 : 2;
             const char *gate = (const char *)m->proj + (size_t)(l.heads + l.kv_heads) * l.dim * es;
             RUN(launch_attn_qk_norm_cache(dt, m->proj, lp.n_in, m->mix, m->kv_pool + lp.k_off, m->kv_pool + lp.v_off, l.q_norm, l.k_norm, c.norm_eps,
                                           d_seq, d_pos, d_bt, mpps, NT, l.heads, l.kv_heads, l.dim, st));
@@ -550,60 +723,130 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
                 RUN(launch_chunked_attention(dt, m->mix, m->kv_pool + lp.k_off, m->kv_pool + lp.v_off, l.sink, gate, lp.n_in, m->mix2, d_seq, d_pos,
                                              d_bt, mpps, NT, l.heads, l.kv_heads, l.dim, l.scale, l.chunk, max_keys, st));
             }
-            RUN(linear(m, m->mix2, l.w_out, m->y, NT, hd, width, st));
+            n_mixed = hd;
+        } else if (l.mixer == B200_MIXER_LATENT) {
+            const int nq = l.heads * (l.dim + l.rot_dim), hv = l.heads * l.vdim;
+            const char *gate = (const char *)m->proj + (size_t)nq * es;
+            char *pool = m->kv_pool + lp.k_off;
+            RUN(launch_latent_prep(dt, m->proj, lp.n_in, 0, l.kv_from < 0 ? nq + hv : -1, m->lqn, m->lqr, pool, l.kv_norm, c.norm_eps, d_seq, d_pos, d_bt,
+                                   mpps, NT, t_pad, l.heads, l.dim, l.rot_dim, l.kv_rank, l.rot_dims, l.rot_base, st));
+            // q into the latent space, head by head: ql[h] = qn[h] . W_uk,h   (rows past the batch's tokens hold whatever the scratch held;
+            // a row of a product depends on its own input row only and those rows are never read)
+            RUN(launch_moe_grouped_gemm(dt, m->lqn, l.w_uk_t, m->lql, d_lat_head, d_lat_n + li, l.heads * tph, l.kv_rank, l.dim, -1, st));
+            const int max_keys = l.window > 0 ? std::min(l.window, mpps * kPageH) : mpps * kPageH;
+            RUN(launch_latent_attention(dt, m->lql, m->lqr, pool, l.sink, m->lol, d_seq, d_pos, d_bt, mpps, NT, t_pad, l.heads, l.kv_rank, l.rot_dim,
+                                        l.scale, l.window, max_keys, st));
+            RUN(launch_moe_grouped_gemm(dt, m->lol, l.w_uv, m->lov, d_lat_head, d_lat_n + li, l.heads * tph, l.vdim, l.kv_rank, -1, st));
+            RUN(launch_latent_gate(dt, m->lov, gate, lp.n_in, m->mix2, NT, t_pad, l.heads, l.vdim, st));
+            n_mixed = hv;
         } else {
             const int hd = l.heads * l.dim, hv = l.heads * l.vdim;
-            const size_t es = f32 ? 4 : 2;
             const char *gate = (const char *)m->proj + (size_t)(2 * hd + hv) * es;
             RUN(launch_gla_decay(dt, m->proj, lp.n_in, 2 * hd + 2 * hv, l.w_decay, l.decay_bias, l.tau, m->f32a, NT, l.decay_rank, hd, st));
             RUN(launch_gla_recurrent(dt, m->proj, lp.n_in, m->f32a, (float *)(m->state_pool + lp.state_off), m->f32b, d_start, d_pos0, d_slot, S,
                                      l.heads, l.dim, l.vdim, st, gla_kinds));
             RUN(launch_gla_output(dt, m->f32b, l.out_norm, c.norm_eps, gate, lp.n_in, m->mix2, NT, l.heads, l.vdim, st));
-            RUN(linear(m, m->mix2, l.w_out, m->y, NT, hv, width, st));
+            n_mixed = hv;
         }
-        RUN(postnorm(m->y, nullptr, nullptr, 0, nullptr, nullptr, l.norm1, trace));
-        if (l.mlp == B200_MLP_MOE) {
-            trace = layer_trace ? layer_trace + (size_t)li * NT * width : nullptr;
-            const int pairs = NT * l.top;
-            // prompt-sized batches of a 16-bit engine: 128-row tiles on the tcgen05 grouped GEMM; otherwise 64-row tiles on mma.sync / SIMT
-            const bool tc = !f32 && pairs >= 1024 && width % 8 == 0 && l.expert_ff % 8 == 0 && width >= 64 && l.expert_ff >= 64;
-            const int tile = tc ? 128 : kMoeTileM;
-            const int max_rows = ((pairs + tile - 1) / tile + std::min(l.experts, pairs)) * tile;
-            const int max_tiles = max_rows / tile;
-            int *sel_expert = m->moe_i, *pair_row = sel_expert + pairs, *row_token = pair_row + pairs, *tile_expert = row_token + max_rows,
-                *n_tiles = tile_expert + max_tiles;
-            float *sel_weight = m->moe_f, *row_weight = sel_weight + pairs, *shared_gate = row_weight + max_rows;
-            const void *h2 = cast_x();
-            // router logits + shared gate, fp32: 16-bit engines multiply the 16-bit copy of x on the tensor cores (products of 16-bit values
-            // are exact in fp32 and the sums are fp32), others -- and widths the tensor-core kernel does not take -- the fp32 kernel
-            // (a decode batch is a single 64-row tile there -- one CTA walking all of K -- so few tokens take the fp32 kernel as well)
-            rc = NT >= 64 ? launch_dense_f32out(dt, h2, l.w_router, m->f32a, NT, l.experts + 1, width, st) : B200_ERR_UNSUPPORTED;
-            if (rc == B200_ERR_UNSUPPORTED) rc = launch_proj_f32(B200_F32, m->x, width, dt, l.w_router, nullptr, m->f32a, l.experts + 1, NT, l.experts + 1, width, st);
-            if (rc != B200_OK) return rc;
-            RUN(launch_moe_route_sigmoid(m->f32a, l.experts + 1, sel_expert, sel_weight, shared_gate, NT, l.experts, l.top, st));
-            RUN(launch_moe_plan(sel_expert, sel_weight, row_token, row_weight, tile_expert, pair_row, n_tiles, NT, l.experts, l.top, tile, st));
-            RUN(launch_moe_gather(dt, m->x, row_token, row_weight, m->xg, n_tiles, max_rows, width, tile, st));
-            if (tc) {
-                RUN(launch_gemm_tc_grouped(m->xg, l.w_up, m->u, max_rows, l.expert_ff, width, l.experts, tile_expert, n_tiles, l.act, dt, st));
-                RUN(launch_gemm_tc_grouped(m->u, l.w_down, m->yrows, max_rows, width, l.expert_ff, l.experts, tile_expert, n_tiles, -1, dt, st));
+        RUN(linear(m, m->mix2, l.w_out, m->y, NT, n_mixed, width, st));
+        if (dyt) {
+            const float *pre = next_pre(li, 0);
+            RUN(residual(true, m->y, nullptr, nullptr, nullptr, nullptr, 0, nullptr, nullptr, l.norm, l.post1, l.ls1, pre, trace));
+            h_normed = pre != nullptr;
+        } else {
+            RUN(postnorm(m->y, nullptr, nullptr, 0, nullptr, nullptr, l.norm1, trace));
+            h_normed = false;
+        }
+        if (l.mlp == B200_MLP_NONE) continue;
+        trace = layer_trace ? layer_trace + (size_t)li * NT * width : nullptr;
+        const void *h2 = dyt ? (const void *)m->h : cast_x();
+        const float *pre = next_pre(li, 1);
+        const int inner_cols = l.gated ? 2 : 1;
+        if (l.mlp == B200_MLP_DENSE) {
+            char *up = (char *)m->us, *act = up;
+            RUN(linear(m, h2, l.w_up, up, NT, width, inner_cols * l.expert_ff, st));
+            if (l.gated) {
+                act = up + (size_t)NT * 2 * l.expert_ff * es;
+                if (l.b_up) RUN(launch_bias_activation(dt, up, l.b_up, NT, 2 * l.expert_ff, -1, st));
+                RUN(launch_gated_activation(dt, up, act, NT, l.expert_ff, l.act, nullptr, 0, st));
             } else {
-                RUN(launch_moe_grouped_gemm(dt, m->xg, l.w_up, m->u, tile_expert, n_tiles, max_tiles, l.expert_ff, width, l.act, st));
-                RUN(launch_moe_grouped_gemm(dt, m->u, l.w_down, m->yrows, tile_expert, n_tiles, max_tiles, width, l.expert_ff, -1, st));
+                RUN(launch_bias_activation(dt, up, l.b_up, NT, l.expert_ff, l.act, st));
             }
-            if (l.shared_ff > 0) {
-                RUN(linear(m, h2, l.w_shared_up, m->us, NT, width, l.shared_ff, st));
+            RUN(linear(m, act, l.w_down, m->ys, NT, l.expert_ff, width, st));
+            if (dyt) RUN(residual(true, m->ys, l.b_down, nullptr, nullptr, nullptr, 0, nullptr, nullptr, l.norm, l.post2, l.ls2, pre, trace));
+            else RUN(residual(true, m->ys, l.b_down, nullptr, nullptr, nullptr, 0, nullptr, nullptr, l.norm, l.norm2, nullptr, nullptr, trace));
+            h_normed = dyt && pre != nullptr;
+            continue;
+        }
+        const int pairs = NT * l.top;
+        const bool softmax = l.route == B200_ROUTE_SOFTMAX;
+        const int outputs = softmax ? l.experts + l.identity : l.experts + 1;
+        // prompt-sized batches of a 16-bit engine: 128-row tiles on the tcgen05 grouped GEMM; otherwise 64-row tiles on mma.sync / SIMT
+        const bool tc = !f32 && pairs >= 1024 && width % 8 == 0 && l.expert_ff % 8 == 0 && width >= 64 && l.expert_ff >= 64;
+        const int tile = tc ? 128 : kMoeTileM;
+        const int max_rows = ((pairs + tile - 1) / tile + std::min(l.experts, pairs)) * tile;
+        const int max_tiles = max_rows / tile;
+        int *sel_expert = m->moe_i, *pair_row = sel_expert + pairs, *row_token = pair_row + pairs, *tile_expert = row_token + max_rows,
+            *n_live = tile_expert + max_tiles;
+        float *sel_weight = m->moe_f, *row_weight = sel_weight + pairs, *shared_gate = row_weight + max_rows;
+        // router logits (+ shared gate), fp32: 16-bit engines multiply the 16-bit copy of the input on the tensor cores (products of 16-bit
+        // values are exact in fp32 and the sums are fp32), others -- and widths the tensor-core kernel does not take -- the fp32 kernel
+        // (a decode batch is a single 64-row tile there -- one CTA walking all of K -- so few tokens take the fp32 kernel as well)
+        rc = NT >= 64 ? launch_dense_f32out(dt, h2, l.w_router, m->f32a, NT, outputs, width, st) : B200_ERR_UNSUPPORTED;
+        if (rc == B200_ERR_UNSUPPORTED)
+            rc = dyt ? launch_proj_f32(dt, m->h, width, dt, l.w_router, nullptr, m->f32a, outputs, NT, outputs, width, st)
+                     : launch_proj_f32(B200_F32, m->x, width, dt, l.w_router, nullptr, m->f32a, outputs, NT, outputs, width, st);
+        if (rc != B200_OK) return rc;
+        if (softmax) RUN(launch_moe_route_softmax(m->f32a, outputs, l.route_bias, sel_expert, sel_weight, NT, outputs, l.top, st));
+        else RUN(launch_moe_route_sigmoid(m->f32a, l.experts + 1, sel_expert, sel_weight, shared_gate, NT, l.experts, l.top, st));
+        RUN(launch_moe_plan(sel_expert, sel_weight, row_token, row_weight, tile_expert, pair_row, n_live, NT, l.experts, l.top, tile, st));
+        if (softmax) RUN(launch_moe_gather_rows(dt, h2, row_token, m->xg, n_live, max_rows, width, tile, st));
+        else RUN(launch_moe_gather(dt, m->x, row_token, row_weight, m->xg, n_live, max_rows, width, tile, st));
+        const int n_up = inner_cols * l.expert_ff;
+        const int up_act = l.gated ? -1 : l.act;
+        char *inner = (char *)m->u;
+        if (tc) RUN(launch_gemm_tc_grouped(m->xg, l.w_up, m->u, max_rows, n_up, width, l.experts, tile_expert, n_live, up_act, dt, st));
+        else RUN(launch_moe_grouped_gemm(dt, m->xg, l.w_up, m->u, tile_expert, n_live, max_tiles, n_up, width, up_act, st));
+        if (l.gated) {
+            inner += (size_t)max_rows * n_up * es;
+            RUN(launch_gated_activation(dt, m->u, inner, max_rows, l.expert_ff, l.act, n_live, tile, st));
+        }
+        if (tc) RUN(launch_gemm_tc_grouped(inner, l.w_down, m->yrows, max_rows, width, l.expert_ff, l.experts, tile_expert, n_live, -1, dt, st));
+        else RUN(launch_moe_grouped_gemm(dt, inner, l.w_down, m->yrows, tile_expert, n_live, max_tiles, width, l.expert_ff, -1, st));
+        if (l.shared_ff > 0) {
+            char *sin = (char *)m->us;
+            RUN(linear(m, h2, l.w_shared_up, m->us, NT, width, inner_cols * l.shared_ff, st));
+            if (l.gated) {
+                sin += (size_t)NT * 2 * l.shared_ff * es;
+                RUN(launch_gated_activation(dt, m->us, sin, NT, l.shared_ff, l.act, nullptr, 0, st));
+            } else {
                 RUN(launch_activation(dt, m->us, (size_t)NT * l.shared_ff, l.act, st));
-                RUN(linear(m, m->us, l.w_shared_down, m->ys, NT, l.shared_ff, width, st));
             }
-            RUN(postnorm(nullptr, m->yrows, pair_row, l.top, l.shared_ff > 0 ? m->ys : nullptr, shared_gate, l.norm2, trace));
+            RUN(linear(m, sin, l.w_shared_down, m->ys, NT, l.shared_ff, width, st));
+        }
+        const void *y_shared = l.shared_ff > 0 ? m->ys : nullptr;
+        if (!softmax) {
+            RUN(postnorm(nullptr, m->yrows, pair_row, l.top, y_shared, shared_gate, l.norm2, trace));
+            h_normed = false;
+        } else {
+            RUN(residual(true, nullptr, nullptr, m->yrows, pair_row, sel_weight, l.top, y_shared, nullptr, l.norm, dyt ? l.post2 : l.norm2,
+                         dyt ? l.ls2 : nullptr, dyt ? pre : nullptr, trace));
+            h_normed = dyt && pre != nullptr;
         }
     }
     if (W > 0) {
         // the wanted rows only: final norm (fp32 and, for 16-bit engines, a 16-bit copy in h), then the LM head with fp32 logits
-        B200_DISPATCH_DTYPE(dt, { final_norm_rows_kernel<T><<<W, 256, 0, st>>>(m->x, d_want, m->final_norm, c.norm_eps, m->xn, f32 ? nullptr : (T *)m->h, width); });
+        B200_DISPATCH_DTYPE(dt, {
+            if (c.final_norm == B200_NORM_DYT_PRE_POST) final_dyt_rows_kernel<T><<<W, 256, 0, st>>>(m->x, d_want, m->final_norm, m->xn, f32 ? nullptr : (T *)m->h, width);
+            else final_norm_rows_kernel<T><<<W, 256, 0, st>>>(m->x, d_want, m->final_norm, c.norm_eps, m->xn, f32 ? nullptr : (T *)m->h, width);
+        });
         rc = launch_dense_f32out(dt, m->h, m->lm_head, logits, W, c.vocab, width, st);
         if (rc == B200_ERR_UNSUPPORTED) rc = launch_proj_f32(B200_F32, m->xn, width, dt, m->lm_head, nullptr, logits, c.vocab, W, c.vocab, width, st);
         if (rc != B200_OK) return rc;
+        if (c.logit_softcap > 0.0f) {
+            const size_t n = (size_t)W * c.vocab;
+            softcap_kernel<<<(unsigned)std::min<size_t>((n + 255) / 256, 148 * 8), 256, 0, st>>>(logits, n, c.logit_softcap);
+        }
     }
 #undef RUN
     return cuda_status("hybrid_forward");

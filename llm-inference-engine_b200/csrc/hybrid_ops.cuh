@@ -17,6 +17,16 @@ int launch_chunked_attention_tiles(int dtype, const void *q, const void *k_pool,
                                    int gate_ld, void *out, const int *tiles, int n_tiles, const int *block_table, int mpps, int heads,
                                    int kv_heads, int dim, float scale, int chunk, cudaStream_t st);
 
+// attention_latent.cu (layouts in the file's header): proj [tokens, ld] holds q at column q_col and, when kv_col >= 0, the down-projection
+int launch_latent_prep(int dtype, const void *proj, int ld, int q_col, int kv_col, void *qn, void *qr, void *pool, const float *kv_norm,
+                       float eps, const int *tok_seq, const int *tok_pos, const int *block_table, int mpps, int tokens, int t_pad, int heads,
+                       int dim, int rot_dim, int kv_rank, int rot_dims, float rot_base, cudaStream_t st);
+int launch_latent_attention(int dtype, const void *ql, const void *qr, const void *pool, const float *sink, void *ol, const int *tok_seq,
+                            const int *tok_pos, const int *block_table, int mpps, int tokens, int t_pad, int heads, int kv_rank, int rot_dim,
+                            float scale, int window, int max_keys, cudaStream_t st, const int *tok_list = nullptr);
+int launch_latent_gate(int dtype, const void *ov, const void *gate_in, int gate_ld, void *out, int tokens, int t_pad, int heads, int vdim,
+                       cudaStream_t st);
+
 // gla.cu
 // decay[t, c] = sigmoid(z)^(1/tau), z = w_decay[c, :] . proj[t, col0 : col0 + rank] + bias[c]   (fp32 from the projection on)
 int launch_gla_decay(int dtype, const void *proj, int ld, int col0, const void *w_decay, const float *bias, float tau, float *decay,
@@ -33,14 +43,25 @@ int launch_gla_output(int dtype, const float *o, const float *w, float eps, cons
 // moe.cu
 int launch_moe_route_sigmoid(const float *logits, int ld, int *sel_expert, float *sel_weight, float *shared_gate, int tokens,
                              int experts, int top, cudaStream_t st);
+// scores = softmax over `outputs` router outputs; choice by score + bias (NULL: none); weights = chosen scores / (their sum + 1e-20)
+int launch_moe_route_softmax(const float *logits, int ld, const float *bias, int *sel_expert, float *sel_weight, int tokens, int outputs,
+                             int top, cudaStream_t st);
 constexpr int kMoeTileM = 64;  // rows of one expert are padded to whole tiles of this many (128 when the tcgen05 grouped GEMM runs)
 // Groups the (token, choice) pairs by expert.  row_token / row_weight [max_rows]: token of every padded row (-1: padding) and its routing
-// weight; tile_expert [max_tiles]; pair_row [tokens*top]: the row each pair landed in; n_tiles: device int.
+// weight; tile_expert [max_tiles]; pair_row [tokens*top]: the row each pair landed in (-1 for a choice >= experts: an identity expert);
+// n_tiles: device int.
 int launch_moe_plan(const int *sel_expert, const float *sel_weight, int *row_token, float *row_weight, int *tile_expert, int *pair_row,
                     int *n_tiles, int tokens, int experts, int top, int tile, cudaStream_t st);
 // xg[row, :] = T(weight[row] * x[token[row], :]) (zeros for padding rows): the routing weight multiplies the expert's INPUT
 int launch_moe_gather(int dtype, const float *x, const int *row_token, const float *row_weight, void *xg, const int *n_tiles,
                       int max_rows, int width, int tile, cudaStream_t st);
+// xg[row, :] = h[token[row], :] of the engine dtype (zeros for padding rows)
+int launch_moe_gather_rows(int dtype, const void *h, const int *row_token, void *xg, const int *n_tiles, int max_rows, int width, int tile,
+                           cudaStream_t st);
+// out[r, c] = act(in[r, c]) * in[r, inner + c], in [rows, 2 * inner]; n_tiles (optional, device): only rows < *n_tiles * tile are live
+int launch_gated_activation(int dtype, const void *in, void *out, int rows, int inner, int act, const int *n_tiles, int tile, cudaStream_t st);
+// in place: x[r, c] = act(x[r, c] + bias[c]); bias NULL: none; act < 0: none
+int launch_bias_activation(int dtype, void *x, const float *bias, size_t rows, int cols, int act, cudaStream_t st);
 // gemm_tc.cu: the same product on tcgen05 for row tiles of 128 (16-bit dtypes, K >= 64 and a multiple of 8; B200_ERR_UNSUPPORTED otherwise)
 int launch_gemm_tc_grouped(const void *a, const void *w, void *c, int max_rows, int N, int K, int experts, const int *tile_expert,
                            const int *n_live, int act, int dtype, cudaStream_t st);

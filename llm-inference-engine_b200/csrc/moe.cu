@@ -7,8 +7,13 @@
 //            the worst-case number of tiles and the surplus CTAs leave at once.
 //   gather:  row <- T(weight * x[token])  -- the weight multiplies the expert's input, which matters for a non-linear expert;
 //   grouped GEMM (x2): up with the activation in the epilogue, then down.
+// A second router form (softmax): scores = softmax(router logits) over all router outputs; the choice is made on score + a per-expert bias,
+// the weights are the chosen experts' scores divided by their sum and multiply the expert's OUTPUT; router outputs past the real experts
+// are identity experts (they return their input and own no rows of the grouped GEMM); experts may be gated: act(gate rows) * up rows.
 // The sum over a token's experts, the shared expert and the post-norm are one kernel of the engine (hybrid.cu).
 #include "hybrid_ops.cuh"
+
+#include <algorithm>
 
 namespace b200 {
 
@@ -41,15 +46,57 @@ __global__ void moe_route_sigmoid_kernel(const float *__restrict__ logits, int l
     if (lane == 0 && shared_gate) shared_gate[t] = 1.0f / (1.0f + expf(-z[experts]));
 }
 
+// one warp per token; `outputs` router outputs (real experts first, then identity experts)
+__global__ void moe_route_softmax_kernel(const float *__restrict__ logits, int ld, const float *__restrict__ bias, int *__restrict__ sel_expert,
+                                         float *__restrict__ sel_weight, int tokens, int outputs, int top) {
+    const int t = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32, lane = threadIdx.x & 31;
+    if (t >= tokens) return;
+    const float *z = logits + (size_t)t * ld;
+    float mx = -INFINITY;
+    for (int e = lane; e < outputs; e += 32) mx = fmaxf(mx, z[e]);
+    mx = warp_max(mx);
+    float den = 0.0f;
+    for (int e = lane; e < outputs; e += 32) den += expf(z[e] - mx);
+    den = warp_sum(den);
+    const float inv = 1.0f / den;
+    float chosen_sum = 0.0f;
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY, best_s = 0.0f;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < outputs; e += 32) {
+            bool taken = false;
+            for (int p = 0; p < k; ++p) taken |= sel_expert[(size_t)t * top + p] == e;
+            const float sc = expf(z[e] - mx) * inv;
+            const float v = sc + (bias ? bias[e] : 0.0f);
+            if (!taken && (v > best || (v == best && e < bi))) best = v, bi = e, best_s = sc;
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o), os = __shfl_xor_sync(0xffffffffu, best_s, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) best = ov, bi = oi, best_s = os;
+        }
+        chosen_sum += best_s;
+        if (lane == 0) {
+            sel_expert[(size_t)t * top + k] = bi;
+            sel_weight[(size_t)t * top + k] = best_s;
+        }
+        __syncwarp();
+    }
+    const float norm = 1.0f / (chosen_sum + 1e-20f);
+    for (int k = lane; k < top; k += 32) sel_weight[(size_t)t * top + k] *= norm;
+}
+
 // one CTA.  Shared: count[E] | offset[E+1] | cursor[E]
 __global__ void __launch_bounds__(1024)
 moe_plan_kernel(const int *__restrict__ sel_expert, const float *__restrict__ sel_weight, int *__restrict__ row_token, float *__restrict__ row_weight,
                 int *__restrict__ tile_expert, int *__restrict__ pair_row, int *__restrict__ n_tiles, int pairs, int experts, int top, int tile) {
+    // choices >= experts (identity experts) own no row: pair_row = -1
     extern __shared__ int si[];
     int *count = si, *offset = si + experts, *cursor = offset + experts + 1;
     for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0, cursor[e] = 0;
     __syncthreads();
-    for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&count[sel_expert[p]], 1);
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x)
+        if (sel_expert[p] < experts) atomicAdd(&count[sel_expert[p]], 1);
     __syncthreads();
     if (threadIdx.x == 0) {
         int at = 0;
@@ -68,6 +115,10 @@ moe_plan_kernel(const int *__restrict__ sel_expert, const float *__restrict__ se
     __syncthreads();
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
         const int e = sel_expert[p];
+        if (e >= experts) {
+            pair_row[p] = -1;
+            continue;
+        }
         const int r = offset[e] + atomicAdd(&cursor[e], 1);
         row_token[r] = p / top;
         row_weight[r] = sel_weight[p];
@@ -102,6 +153,47 @@ moe_gather_kernel(const float *__restrict__ x, const int *__restrict__ row_token
     }
     for (int c = threadIdx.x; c < width; c += blockDim.x)
         xg[(size_t)r * width + c] = Elem<T>::from_f(t >= 0 ? w * x[(size_t)t * width + c] : 0.0f);
+}
+
+// xg[row, :] = h[token[row], :] (zeros for padding rows): the expert reads the token's row as it is, the weight goes on its output
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_gather_rows_kernel(const T *__restrict__ h, const int *__restrict__ row_token, T *__restrict__ xg, const int *__restrict__ n_tiles, int width,
+                       int tile) {
+    const int r = blockIdx.x;
+    if (r >= *n_tiles * tile) return;
+    const int t = row_token[r];
+    constexpr int V = Elem<T>::kVec;
+    if (width % V == 0 && ((reinterpret_cast<size_t>(h) | reinterpret_cast<size_t>(xg)) & 15) == 0) {
+        for (int c = threadIdx.x * V; c < width; c += blockDim.x * V)
+            st_v4(xg + (size_t)r * width + c, t >= 0 ? ld_v4(h + (size_t)t * width + c) : make_uint4(0, 0, 0, 0));
+        return;
+    }
+    for (int c = threadIdx.x; c < width; c += blockDim.x) xg[(size_t)r * width + c] = t >= 0 ? h[(size_t)t * width + c] : Elem<T>::from_f(0.0f);
+}
+
+// out[r, c] = act(in[r, c]) * in[r, inner + c] for rows r < *n_rows_live (all `rows` when n_tiles is NULL); in [rows, 2 * inner]
+template <typename T>
+__global__ void gated_activation_kernel(const T *__restrict__ in, T *__restrict__ out, int rows, int inner, int act, const int *__restrict__ n_tiles,
+                                        int tile) {
+    const int live = n_tiles ? min(rows, *n_tiles * tile) : rows;
+    const size_t n = (size_t)live * inner;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / inner, c = i - r * inner;
+        const float g = Elem<T>::to_f(in[r * 2 * inner + c]), u = Elem<T>::to_f(in[r * 2 * inner + inner + c]);
+        out[i] = Elem<T>::from_f(act_apply(g, act) * u);
+    }
+}
+
+// in place: x[r, c] = act(x[r, c] + bias[c]) (bias may be NULL, act < 0: none)
+template <typename T>
+__global__ void bias_activation_kernel(T *__restrict__ x, const float *__restrict__ bias, size_t rows, int cols, int act) {
+    const size_t n = rows * cols;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float v = Elem<T>::to_f(x[i]);
+        if (bias) v += bias[i % cols];
+        x[i] = Elem<T>::from_f(act >= 0 ? act_apply(v, act) : v);
+    }
 }
 
 // SIMT grouped GEMM, 64 x 64 tile, fp32 accumulation.  The tensor-core path of the dense linears does not apply: an expert's rows are
@@ -284,6 +376,36 @@ int launch_moe_route_sigmoid(const float *logits, int ld, int *sel_expert, float
     if (tokens == 0) return B200_OK;
     moe_route_sigmoid_kernel<<<(tokens + 3) / 4, 128, 0, st>>>(logits, ld, sel_expert, sel_weight, shared_gate, tokens, experts, top);
     return cuda_status("moe_route launch");
+}
+
+int launch_moe_route_softmax(const float *logits, int ld, const float *bias, int *sel_expert, float *sel_weight, int tokens, int outputs,
+                             int top, cudaStream_t st) {
+    if (tokens == 0) return B200_OK;
+    moe_route_softmax_kernel<<<(tokens + 3) / 4, 128, 0, st>>>(logits, ld, bias, sel_expert, sel_weight, tokens, outputs, top);
+    return cuda_status("moe_route (softmax) launch");
+}
+
+int launch_moe_gather_rows(int dtype, const void *h, const int *row_token, void *xg, const int *n_tiles, int max_rows, int width, int tile,
+                           cudaStream_t st) {
+    if (max_rows == 0) return B200_OK;
+    B200_DISPATCH_DTYPE(dtype, { moe_gather_rows_kernel<T><<<max_rows, 128, 0, st>>>((const T *)h, row_token, (T *)xg, n_tiles, width, tile); });
+    return cuda_status("moe_gather_rows launch");
+}
+
+int launch_gated_activation(int dtype, const void *in, void *out, int rows, int inner, int act, const int *n_tiles, int tile, cudaStream_t st) {
+    if (rows == 0 || inner == 0) return B200_OK;
+    const size_t n = (size_t)rows * inner;
+    const unsigned grid = (unsigned)std::min<size_t>((n + 255) / 256, 148 * 16);
+    B200_DISPATCH_DTYPE(dtype, { gated_activation_kernel<T><<<grid, 256, 0, st>>>((const T *)in, (T *)out, rows, inner, act, n_tiles, tile); });
+    return cuda_status("gated_activation launch");
+}
+
+int launch_bias_activation(int dtype, void *x, const float *bias, size_t rows, int cols, int act, cudaStream_t st) {
+    if (rows == 0 || cols == 0) return B200_OK;
+    const size_t n = rows * cols;
+    const unsigned grid = (unsigned)std::min<size_t>((n + 255) / 256, 148 * 16);
+    B200_DISPATCH_DTYPE(dtype, { bias_activation_kernel<T><<<grid, 256, 0, st>>>((T *)x, bias, rows, cols, act); });
+    return cuda_status("bias_activation launch");
 }
 
 int launch_moe_plan(const int *sel_expert, const float *sel_weight, int *row_token, float *row_weight, int *tile_expert, int *pair_row,

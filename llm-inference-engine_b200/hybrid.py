@@ -15,28 +15,34 @@ class HybridDecoder:
     """layers: list of dicts with the integer / float fields of b200_hybrid_layer_t and device tensors under the weight names.
     The tensors are kept alive by this object."""
 
-    def __init__(self, width, vocab, eps, layers, embedding, final_norm, lm_head, dtype, device, max_tokens, max_seqs, max_pages_per_seq):
+    def __init__(self, width, vocab, eps, layers, embedding, final_norm, lm_head, dtype, device, max_tokens, max_seqs, max_pages_per_seq,
+                 embed_scale=1.0, logit_softcap=0.0, final_norm_kind=0):
         import torch
 
         m = _mod()
         self.device = torch.device(device)
         self.torch_dtype = dtype
         code = {torch.float32: m.F32, torch.float16: m.F16, torch.bfloat16: m.BF16}[dtype]
-        self.cfg = m.HybridConfig(int(width), int(vocab), len(layers), code, float(eps), int(max_tokens), int(max_seqs), int(max_pages_per_seq))
+        self.cfg = m.HybridConfig(int(width), int(vocab), len(layers), code, float(eps), int(max_tokens), int(max_seqs), int(max_pages_per_seq),
+                                  float(embed_scale), float(logit_softcap), int(final_norm_kind))
         self.handle = m.lib().b200_hybrid_create(C.byref(self.cfg))
         if not self.handle:
             raise m.B200Error(m.lib().b200_last_error_string().decode())
         self._keep = [layers, embedding, final_norm, lm_head]
         self.layers = layers
-        ints = ("mixer", "heads", "kv_heads", "dim", "vdim", "chunk", "decay_rank", "mlp", "experts", "top", "expert_ff", "shared_ff", "act")
+        ints = ("mixer", "heads", "kv_heads", "dim", "vdim", "chunk", "decay_rank", "mlp", "experts", "top", "expert_ff", "shared_ff", "act",
+                "norm", "window", "kv_rank", "rot_dim", "rot_dims", "route", "identity", "gated")
         tensors = ("w_in", "w_out", "q_norm", "k_norm", "sink", "w_decay", "decay_bias", "out_norm", "norm1", "norm2", "w_router", "w_up",
-                   "w_down", "w_shared_up", "w_shared_down")
-        f32_vectors = {"q_norm", "k_norm", "sink", "decay_bias", "out_norm", "norm1", "norm2"}
+                   "w_down", "w_shared_up", "w_shared_down", "kv_norm", "w_uk_t", "w_uv", "pre1", "post1", "pre2", "post2", "ls1", "ls2",
+                   "route_bias", "b_up", "b_down")
+        f32_vectors = {"q_norm", "k_norm", "sink", "decay_bias", "out_norm", "norm1", "norm2", "kv_norm", "pre1", "post1", "pre2", "post2",
+                       "ls1", "ls2", "route_bias", "b_up", "b_down"}
         for i, spec in enumerate(layers):
             lw = m.HybridLayer()
             for k in ints:
                 setattr(lw, k, int(spec.get(k, 0)))
             lw.scale, lw.tau = float(spec.get("scale", 1.0)), float(spec.get("tau", 1.0))
+            lw.rot_base, lw.kv_from = float(spec.get("rot_base", 0.0)), int(spec.get("kv_from", -1))
             for k in tensors:
                 t = spec.get(k)
                 if t is not None:
