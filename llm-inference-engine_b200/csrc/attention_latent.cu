@@ -189,6 +189,195 @@ latent_attn_kernel(const T *__restrict__ ql, const T *__restrict__ qr, const T *
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------------------------
+// Tensor-core kernel (16-bit engines; kv_rank and rot_dim multiples of 16): one CTA = a tile of <= 64 query rows that share their keys,
+// four warps of 16 rows each.  Two kinds of tile:
+//   by_head == 0: 64 consecutive tokens of ONE sequence x one head (blockIdx.y)          -- prompt portions;
+//   by_head == 1: ONE token x 64 consecutive heads (blockIdx.y * 64 ...)                  -- decoded tokens of many-headed layers: the
+//                 heads share every key row, so the window is read once per 64 heads instead of once per head.
+// A key tile is one page (64 positions) of rows [c | kr]: it arrives by cp.async into a two-stage ring, S = Q K^T over all kv_rank +
+// rot_dim columns and O += P V over value columns [v0, v0 + 16 NV) OF THE SAME TILE run on mma.sync.m16n8k16 with fp32 accumulators, the
+// softmax is the online form in fp32.  blockIdx.z selects a block of 128 value columns when kv_rank > 128 (the scores are formed again
+// per block).  The sink enters as the INITIAL running state (max = sink, sum = 1, nothing accumulated): a key with that logit and a
+// zero value.  The mask is evaluated per element: a tile of queries may straddle a window edge; the key tiles walked run from the
+// window start of the tile's first query to its last query.  Rows of a key tile past the tile's last query are zeroed, not fetched:
+// they may belong to a page's previous owner, and 0 x NaN is NaN on the tensor core.
+// tiles: int4 per tile {sequence, first packed row, rows (1..64; by_head: unused), position of the first row}.
+namespace {
+__device__ __forceinline__ void lat_cp_async16(void *smem, const void *gmem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void lat_ldsm_x4(unsigned &r0, unsigned &r1, unsigned &r2, unsigned &r3, const void *p) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void lat_ldsm_x4_trans(unsigned &r0, unsigned &r1, unsigned &r2, unsigned &r3, const void *p) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+template <typename T> __device__ __forceinline__ void lat_mma(float *c, const unsigned *a, unsigned b0, unsigned b1);
+template <> __device__ __forceinline__ void lat_mma<__nv_bfloat16>(float *c, const unsigned *a, unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <> __device__ __forceinline__ void lat_mma<__half>(float *c, const unsigned *a, unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <typename T> __device__ __forceinline__ unsigned lat_pack2(float lo, float hi);
+template <> __device__ __forceinline__ unsigned lat_pack2<__nv_bfloat16>(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned *>(&v);
+}
+template <> __device__ __forceinline__ unsigned lat_pack2<__half>(float lo, float hi) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<unsigned *>(&v);
+}
+// element (row, col) of a [rows][ld] 16-bit tile (ld a multiple of 64) whose 16-byte pieces are XOR-swizzled by the row within groups of
+// eight pieces: conflict-free ldmatrix
+__device__ __forceinline__ int lat_swz(int row, int col, int ld) { return row * ld + ((((col >> 3) ^ (row & 7)) << 3) | (col & 7)); }
+constexpr int kLatTileQ = 64;
+}  // namespace
+
+template <typename T, int NV>
+__global__ void __launch_bounds__(128)
+latent_attn_mma_kernel(const T *__restrict__ ql, const T *__restrict__ qr, const T *__restrict__ pool, const float *__restrict__ sink,
+                       T *__restrict__ ol, const int4 *__restrict__ tiles, const int *__restrict__ block_table, int mpps, int t_pad, int heads,
+                       int kv_rank, int rot_dim, int ld, float scale, int window, int by_head) {
+    extern __shared__ __align__(16) unsigned char smraw[];
+    T *qs = reinterpret_cast<T *>(smraw);  // [64][ld]
+    T *ks = qs + kLatTileQ * ld;           // [2][64][ld]
+    const int4 tile = tiles[blockIdx.x];
+    const int dk = kv_rank + rot_dim, pieces = dk / 8;
+    const int row0 = tile.y, pos0 = tile.w;
+    const int h0 = by_head ? blockIdx.y * kLatTileQ : blockIdx.y;
+    const int nrows = by_head ? min(kLatTileQ, heads - h0) : tile.z;
+    const int v0 = blockIdx.z * 128;
+    const int *bt = block_table + (size_t)tile.x * mpps;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
+    const int last = by_head ? pos0 : pos0 + nrows - 1;
+    const int first = window > 0 ? max(0, pos0 - window + 1) : 0;
+    const int tile_lo = first / kPageL, tile_hi = last / kPageL;
+
+    auto load_kv = [&](int kt, int stage) {
+        const T *src = pool + (size_t)bt[kt] * kPageL * dk;
+        T *dst = ks + stage * kPageL * ld;
+        for (int i = threadIdx.x; i < kPageL * pieces; i += 128) {
+            const int r = i / pieces, c = (i - r * pieces) * 8;
+            if (kt * kPageL + r <= last) lat_cp_async16(dst + lat_swz(r, c, ld), src + (size_t)r * dk + c);
+            else *reinterpret_cast<uint4 *>(dst + lat_swz(r, c, ld)) = make_uint4(0, 0, 0, 0);
+        }
+    };
+    load_kv(tile_lo, 0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    for (int i = threadIdx.x; i < kLatTileQ * pieces; i += 128) {
+        const int r = i / pieces, c = (i - r * pieces) * 8;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < nrows) {
+            const int t = by_head ? row0 : row0 + r, h = by_head ? h0 + r : h0;
+            v = c < kv_rank ? ld_v4(ql + ((size_t)h * t_pad + t) * kv_rank + c) : ld_v4(qr + ((size_t)t * heads + h) * rot_dim + (c - kv_rank));
+        }
+        *reinterpret_cast<uint4 *>(qs + lat_swz(r, c, ld)) = v;
+    }
+
+    constexpr float kLog2e = 1.4426950408889634f;
+    const float sl2 = scale * kLog2e;
+    // rows gid and gid + 8 of this warp's 16
+    const int r_a = warp * 16 + gid, r_b = r_a + 8;
+    const int p_a = by_head ? pos0 : pos0 + r_a, p_b = by_head ? pos0 : pos0 + r_b;
+    const int lo_a = window > 0 ? p_a - window : -1, lo_b = window > 0 ? p_b - window : -1;  // visible keys: lo < key <= p
+    float m_a, m_b, l_a, l_b;
+    if (sink) {
+        m_a = sink[by_head ? min(h0 + r_a, heads - 1) : h0] * kLog2e, m_b = sink[by_head ? min(h0 + r_b, heads - 1) : h0] * kLog2e;
+        l_a = l_b = tig == 0 ? 1.0f : 0.0f;  // the sum is kept per lane and joined at the end
+    } else {
+        m_a = m_b = -1e30f, l_a = l_b = 0.0f;
+    }
+    float o[2 * NV][4];
+#pragma unroll
+    for (int j = 0; j < 2 * NV; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
+
+    for (int kt = tile_lo; kt <= tile_hi; ++kt) {
+        const int stage = (kt - tile_lo) & 1;
+        if (kt < tile_hi) load_kv(kt + 1, stage ^ 1);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncthreads();
+        const T *kst = ks + stage * kPageL * ld;
+        float s[8][4];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
+#pragma unroll 2
+        for (int kk = 0; kk < dk / 16; ++kk) {
+            unsigned qf[4];
+            lat_ldsm_x4(qf[0], qf[1], qf[2], qf[3], qs + lat_swz(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, kk * 16 + (lane >> 4) * 8, ld));
+#pragma unroll
+            for (int jp = 0; jp < 4; ++jp) {  // two key blocks of 8 per ldmatrix
+                unsigned b0, b1, b2, b3;
+                lat_ldsm_x4(b0, b1, b2, b3, kst + lat_swz(jp * 16 + (lane & 7) + (lane >> 4) * 8, kk * 16 + ((lane >> 3) & 1) * 8, ld));
+                lat_mma<T>(s[2 * jp], qf, b0, b1);
+                lat_mma<T>(s[2 * jp + 1], qf, b2, b3);
+            }
+        }
+        // scale, mask, running max
+        float mx_a = m_a, mx_b = m_b;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int key = kt * kPageL + j * 8 + tig * 2 + e;
+                s[j][e] = (key <= p_a && key > lo_a) ? s[j][e] * sl2 : -INFINITY;
+                s[j][2 + e] = (key <= p_b && key > lo_b) ? s[j][2 + e] * sl2 : -INFINITY;
+                mx_a = fmaxf(mx_a, s[j][e]);
+                mx_b = fmaxf(mx_b, s[j][2 + e]);
+            }
+        }
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+        const float f_a = exp2f(m_a - mx_a), f_b = exp2f(m_b - mx_b);
+        m_a = mx_a, m_b = mx_b;
+        float sum_a = 0.0f, sum_b = 0.0f;
+        unsigned pf[4][4];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float e0 = exp2f(s[j][0] - m_a), e1 = exp2f(s[j][1] - m_a), e2 = exp2f(s[j][2] - m_b), e3 = exp2f(s[j][3] - m_b);
+            sum_a += e0 + e1, sum_b += e2 + e3;
+            pf[j >> 1][(j & 1) * 2] = lat_pack2<T>(e0, e1);
+            pf[j >> 1][(j & 1) * 2 + 1] = lat_pack2<T>(e2, e3);
+        }
+        l_a = l_a * f_a + sum_a, l_b = l_b * f_b + sum_b;  // per-lane partial sums; joined across the row's four lanes at the end
+#pragma unroll
+        for (int j = 0; j < 2 * NV; ++j) o[j][0] *= f_a, o[j][1] *= f_a, o[j][2] *= f_b, o[j][3] *= f_b;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {  // 16 keys per step; the values are columns [v0, v0 + 16 NV) of the key tile itself
+#pragma unroll
+            for (int jp = 0; jp < NV; ++jp) {
+                unsigned b0, b1, b2, b3;
+                lat_ldsm_x4_trans(b0, b1, b2, b3, kst + lat_swz(kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, v0 + jp * 16 + (lane >> 4) * 8, ld));
+                lat_mma<T>(o[2 * jp], pf[kk], b0, b1);
+                lat_mma<T>(o[2 * jp + 1], pf[kk], b2, b3);
+            }
+        }
+        __syncthreads();  // everybody is done with this stage before the next iteration's prefetch overwrites it
+    }
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+    const float i_a = 1.0f / l_a, i_b = 1.0f / l_b;
+    T *out_a = ol + (by_head ? ((size_t)(h0 + r_a) * t_pad + row0) : ((size_t)h0 * t_pad + row0 + r_a)) * kv_rank + v0;
+    T *out_b = ol + (by_head ? ((size_t)(h0 + r_b) * t_pad + row0) : ((size_t)h0 * t_pad + row0 + r_b)) * kv_rank + v0;
+#pragma unroll
+    for (int j = 0; j < 2 * NV; ++j) {
+        const int c = j * 8 + tig * 2;
+        if (r_a < nrows) *reinterpret_cast<unsigned *>(out_a + c) = lat_pack2<T>(o[j][0] * i_a, o[j][1] * i_a);
+        if (r_b < nrows) *reinterpret_cast<unsigned *>(out_b + c) = lat_pack2<T>(o[j][2] * i_b, o[j][3] * i_b);
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 latent_gate_kernel(const T *__restrict__ ov, const T *__restrict__ gate_in, int gate_ld, T *__restrict__ out, int t_pad, int heads, int vdim) {
@@ -233,6 +422,52 @@ int launch_latent_attention(int dtype, const void *ql, const void *qr, const voi
                                                                            window, max_keys, (int)part, tok_list);
     });
     return cuda_status("latent_attention launch");
+}
+
+bool latent_attention_tiles_supported(int dtype, int kv_rank, int rot_dim) {
+    const int ld = (kv_rank + rot_dim + 63) / 64 * 64;
+    return dtype != B200_F32 && kv_rank % 16 == 0 && rot_dim % 16 == 0 && (kv_rank <= 128 || kv_rank % 128 == 0) &&
+           (size_t)3 * kLatTileQ * ld * 2 <= 227 * 1024;
+}
+
+template <typename T, int NV>
+static int launch_latent_mma_t(const void *ql, const void *qr, const void *pool, const float *sink, void *ol, const int *tiles, dim3 grid,
+                               const int *block_table, int mpps, int t_pad, int heads, int kv_rank, int rot_dim, float scale, int window, int by_head,
+                               cudaStream_t st) {
+    const int ld = (kv_rank + rot_dim + 63) / 64 * 64;
+    const size_t smem = (size_t)3 * kLatTileQ * ld * sizeof(T);
+    cudaFuncSetAttribute(latent_attn_mma_kernel<T, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    latent_attn_mma_kernel<T, NV><<<grid, 128, smem, st>>>((const T *)ql, (const T *)qr, (const T *)pool, sink, (T *)ol, (const int4 *)tiles,
+                                                           block_table, mpps, t_pad, heads, kv_rank, rot_dim, ld, scale, window, by_head);
+    return cuda_status("latent_attention (tensor core) launch");
+}
+
+int launch_latent_attention_tiles(int dtype, const void *ql, const void *qr, const void *pool, const float *sink, void *ol, const int *tiles,
+                                  int n_tiles, const int *block_table, int mpps, int t_pad, int heads, int kv_rank, int rot_dim, float scale,
+                                  int window, int by_head, cudaStream_t st) {
+    if (n_tiles == 0) return B200_OK;
+    if (!latent_attention_tiles_supported(dtype, kv_rank, rot_dim)) {
+        set_error("latent_attention tiles: 16-bit dtypes, kv_rank and rot_dim multiples of 16, kv_rank <= 128 or a multiple of 128");
+        return B200_ERR_UNSUPPORTED;
+    }
+    const dim3 grid(n_tiles, by_head ? (heads + kLatTileQ - 1) / kLatTileQ : heads, kv_rank > 128 ? kv_rank / 128 : 1);
+    const int nv = kv_rank > 128 ? 8 : kv_rank / 16;
+#define B200_LAT_TILES(TT)                                                                                                                       \
+    switch (nv) {                                                                                                                                \
+        case 1: return launch_latent_mma_t<TT, 1>(ql, qr, pool, sink, ol, tiles, grid, block_table, mpps, t_pad, heads, kv_rank, rot_dim, scale, window, by_head, st); \
+        case 2: return launch_latent_mma_t<TT, 2>(ql, qr, pool, sink, ol, tiles, grid, block_table, mpps, t_pad, heads, kv_rank, rot_dim, scale, window, by_head, st); \
+        case 3: return launch_latent_mma_t<TT, 3>(ql, qr, pool, sink, ol, tiles, grid, block_table, mpps, t_pad, heads, kv_rank, rot_dim, scale, window, by_head, st); \
+        case 4: return launch_latent_mma_t<TT, 4>(ql, qr, pool, sink, ol, tiles, grid, block_table, mpps, t_pad, heads, kv_rank, rot_dim, scale, window, by_head, st); \
+        case 5: return launch_latent_mma_t<TT, 5>(ql, qr, pool, sink, ol, tiles, grid, block_table, mpps, t_pad, heads, kv_rank, rot_dim, scale, window, by_head, st); \
+        case 6: return launch_latent_mma_t<TT, 6>(ql, qr, pool, sink, ol, tiles, grid, block_table, mpps, t_pad, heads, kv_rank, rot_dim, scale, window, by_head, st); \
+        case 7: return launch_latent_mma_t<TT, 7>(ql, qr, pool, sink, ol, tiles, grid, block_table, mpps, t_pad, heads, kv_rank, rot_dim, scale, window, by_head, st); \
+        default: return launch_latent_mma_t<TT, 8>(ql, qr, pool, sink, ol, tiles, grid, block_table, mpps, t_pad, heads, kv_rank, rot_dim, scale, window, by_head, st); \
+    }
+    if (dtype == B200_BF16) {
+        B200_LAT_TILES(__nv_bfloat16)
+    }
+    B200_LAT_TILES(__half)
+#undef B200_LAT_TILES
 }
 
 int launch_latent_gate(int dtype, const void *ov, const void *gate_in, int gate_ld, void *out, int tokens, int t_pad, int heads, int vdim,

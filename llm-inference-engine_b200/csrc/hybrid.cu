@@ -27,6 +27,7 @@
 namespace b200 {
 
 constexpr int kPageH = B200_KV_PAGE_SIZE;
+constexpr int kLatentHeadsPerTile = 16;  // latent layers with at least this many heads run a decoded token's heads as one tensor-core tile
 static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
 template <typename T>
@@ -407,9 +408,10 @@ Carve carve(const b200_hybrid *m) {
     k.lqn = align256(lqn * es), k.lqr = align256(lqr * es), k.lql = align256(lql * es), k.lov = align256(lov * es);
     // meta: attention tiles [4 * (T/64 + S), padded] | ids | tok_seq | tok_pos | want | short-portion token list [T each] | seq_start [S+1] |
     //       pos0 | slot [S each] | block table [S * mpps]
-    //       | latent mixers: head of every row tile [heads * t_pad / 64] | live row tiles per layer [layers]
+    //       | latent mixers: one-token tiles of the short portions [4 * T] | head of every row tile of 64 and of 128 [heads * t_pad / 64,
+    //         heads * t_pad / 128] | live row tiles per layer, of 64 and of 128 [layers each]
     k.meta = align256((4 * (T / 64 + (size_t)c.max_seqs + 1) + 5 * T + 3 * (size_t)c.max_seqs + 1 + (size_t)c.max_seqs * c.max_pages_per_seq +
-                       lheads * (t_pad / 64) + (size_t)c.num_layers) * 4);
+                       (lheads ? 4 * T : 0) + 2 * lheads * (t_pad / 64) + 2 * (size_t)c.num_layers) * 4);
     // moe ints: sel_expert | pair_row [T*top each] | row_token [rows] | tile_expert [rows / tile] | n_tiles
     k.moe_i = align256((2 * T * top + rows + rows / kMoeTileM + 4) * 4);
     // moe floats: sel_weight [T*top] | row_weight [rows] | shared_gate [T]
@@ -602,18 +604,31 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
 
     // ---- batch description: checked on the host, shipped in one copy
     std::vector<int> &hm = m->host_meta;
-    const size_t n_tile_ints = 4 * ((size_t)NT / 64 + S + 1);
-    // latent mixers: their per-head products are grouped GEMMs over [heads, t_pad, *] with row tiles of 64; tile i belongs to head i / tph
-    const int t_pad = (NT + kMoeTileM - 1) / kMoeTileM * kMoeTileM, tph = t_pad / kMoeTileM;
+    // latent mixers: their per-head products are grouped GEMMs over [heads, t_pad, *]; row tile i belongs to head i / (tiles per head).
+    // Prompt-sized batches of a 16-bit engine take 128-row tiles on the tcgen05 grouped GEMM, others 64-row tiles on mma.sync / SIMT.
     int lat_heads = 0;
-    for (int i = 0; i < c.num_layers; ++i)
-        if (m->layers[i].mixer == B200_MIXER_LATENT) lat_heads = std::max(lat_heads, m->layers[i].heads);
-    hm.assign(n_tile_ints + (size_t)5 * NT + 3 * S + 1 + (size_t)S * mpps + (size_t)lat_heads * tph + c.num_layers, 0);
-    int *h_tiles = hm.data(), *h_ids = h_tiles + n_tile_ints, *h_seq = h_ids + NT, *h_pos = h_seq + NT, *h_want = h_pos + NT, *h_short = h_want + NT,
-        *h_start = h_short + NT, *h_pos0 = h_start + S + 1, *h_slot = h_pos0 + S, *h_bt = h_slot + S, *h_lat_head = h_bt + (size_t)S * mpps,
-        *h_lat_n = h_lat_head + (size_t)lat_heads * tph;
+    bool lat_by_head = false;  // some latent layer runs its short portions as one-token tiles over 64 heads
+    for (int i = 0; i < c.num_layers; ++i) {
+        const b200_hybrid_layer_t &l = m->layers[i];
+        if (l.mixer != B200_MIXER_LATENT) continue;
+        lat_heads = std::max(lat_heads, l.heads);
+        lat_by_head |= l.heads >= kLatentHeadsPerTile && latent_attention_tiles_supported(c.dtype, l.kv_rank, l.rot_dim);
+    }
+    const bool lat_tc = c.dtype != B200_F32 && NT >= 256;
+    const int t_pad = lat_tc ? (NT + 127) / 128 * 128 : (NT + kMoeTileM - 1) / kMoeTileM * kMoeTileM;
+    const int tph = t_pad / kMoeTileM, tph128 = lat_tc ? t_pad / 128 : 0;
+    const size_t n_tile_ints = 4 * ((size_t)NT / 64 + S + 1), n_stile_ints = lat_by_head ? (size_t)4 * NT : 0;
+    hm.assign(n_tile_ints + n_stile_ints + (size_t)5 * NT + 3 * S + 1 + (size_t)S * mpps + (size_t)lat_heads * (tph + tph128) + 2 * c.num_layers, 0);
+    int *h_tiles = hm.data(), *h_stiles = h_tiles + n_tile_ints, *h_ids = h_stiles + n_stile_ints, *h_seq = h_ids + NT, *h_pos = h_seq + NT,
+        *h_want = h_pos + NT, *h_short = h_want + NT, *h_start = h_short + NT, *h_pos0 = h_start + S + 1, *h_slot = h_pos0 + S, *h_bt = h_slot + S,
+        *h_lat_head = h_bt + (size_t)S * mpps, *h_lat_head128 = h_lat_head + (size_t)lat_heads * tph,
+        *h_lat_n = h_lat_head128 + (size_t)lat_heads * tph128, *h_lat_n128 = h_lat_n + c.num_layers;
     for (int i = 0; i < lat_heads * tph; ++i) h_lat_head[i] = i / tph;
-    for (int i = 0; i < c.num_layers; ++i) h_lat_n[i] = m->layers[i].mixer == B200_MIXER_LATENT ? m->layers[i].heads * tph : 0;
+    for (int i = 0; i < lat_heads * tph128; ++i) h_lat_head128[i] = i / tph128;
+    for (int i = 0; i < c.num_layers; ++i) {
+        const bool lat = m->layers[i].mixer == B200_MIXER_LATENT;
+        h_lat_n[i] = lat ? m->layers[i].heads * tph : 0, h_lat_n128[i] = lat ? m->layers[i].heads * tph128 : 0;
+    }
     // prompt portions go to the tensor-core attention in tiles of <= 64 consecutive tokens, short ones (decoded tokens) to the per-token kernel
     constexpr int kShortPortion = 8;
     int n_tiles = 0, n_short = 0, gla_kinds = 0;
@@ -631,7 +646,13 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
         }
         for (int t = t0; t < t1; ++t) h_seq[t] = s, h_pos[t] = b->seq_pos0[s] + (t - t0);
         if (t1 - t0 < kShortPortion) {
-            for (int t = t0; t < t1; ++t) h_short[n_short++] = t;
+            for (int t = t0; t < t1; ++t) {
+                if (lat_by_head) {
+                    int *tl = h_stiles + 4 * n_short;
+                    tl[0] = s, tl[1] = t, tl[2] = 1, tl[3] = h_pos[t];
+                }
+                h_short[n_short++] = t;
+            }
         } else {
             for (int t = t0; t < t1; t += 64, ++n_tiles) {
                 int *tl = h_tiles + 4 * n_tiles;
@@ -653,9 +674,10 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
     cudaStream_t st = as_stream(stream);
     NvtxRange range("hybrid_forward");
     if (cudaMemcpyAsync(m->meta, hm.data(), hm.size() * sizeof(int), cudaMemcpyHostToDevice, st) != cudaSuccess) return cuda_status("hybrid_forward meta copy");
-    const int *d_tiles = m->meta, *d_ids = d_tiles + n_tile_ints, *d_seq = d_ids + NT, *d_pos = d_seq + NT, *d_want = d_pos + NT, *d_short = d_want + NT,
-              *d_start = d_short + NT, *d_pos0 = d_start + S + 1, *d_slot = d_pos0 + S, *d_bt = d_slot + S, *d_lat_head = d_bt + (size_t)S * mpps,
-              *d_lat_n = d_lat_head + (size_t)lat_heads * tph;
+    const int *d_tiles = m->meta, *d_stiles = d_tiles + n_tile_ints, *d_ids = d_stiles + n_stile_ints, *d_seq = d_ids + NT, *d_pos = d_seq + NT,
+              *d_want = d_pos + NT, *d_short = d_want + NT, *d_start = d_short + NT, *d_pos0 = d_start + S + 1, *d_slot = d_pos0 + S, *d_bt = d_slot + S,
+              *d_lat_head = d_bt + (size_t)S * mpps, *d_lat_head128 = d_lat_head + (size_t)lat_heads * tph,
+              *d_lat_n = d_lat_head128 + (size_t)lat_heads * tph128, *d_lat_n128 = d_lat_n + c.num_layers;
 
     const int dt = c.dtype, width = c.width;
     const bool f32 = dt == B200_F32;
@@ -730,13 +752,31 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
             char *pool = m->kv_pool + lp.k_off;
             RUN(launch_latent_prep(dt, m->proj, lp.n_in, 0, l.kv_from < 0 ? nq + hv : -1, m->lqn, m->lqr, pool, l.kv_norm, c.norm_eps, d_seq, d_pos, d_bt,
                                    mpps, NT, t_pad, l.heads, l.dim, l.rot_dim, l.kv_rank, l.rot_dims, l.rot_base, st));
-            // q into the latent space, head by head: ql[h] = qn[h] . W_uk,h   (rows past the batch's tokens hold whatever the scratch held;
-            // a row of a product depends on its own input row only and those rows are never read)
-            RUN(launch_moe_grouped_gemm(dt, m->lqn, l.w_uk_t, m->lql, d_lat_head, d_lat_n + li, l.heads * tph, l.kv_rank, l.dim, -1, st));
+            // the per-head products: rows past the batch's tokens hold whatever the scratch held; a row of a product depends on its own
+            // input row only and those rows are never read
+            auto head_product = [&](const void *a, const void *w, void *out, int N, int K) -> int {
+                if (lat_tc) {
+                    const int r = launch_gemm_tc_grouped(a, w, out, l.heads * t_pad, N, K, l.heads, d_lat_head128, d_lat_n128 + li, -1, dt, st);
+                    if (r != B200_ERR_UNSUPPORTED) return r;
+                }
+                return launch_moe_grouped_gemm(dt, a, w, out, d_lat_head, d_lat_n + li, l.heads * tph, N, K, -1, st);
+            };
+            RUN(head_product(m->lqn, l.w_uk_t, m->lql, l.kv_rank, l.dim));  // q into the latent space: ql[h] = qn[h] . W_uk,h
             const int max_keys = l.window > 0 ? std::min(l.window, mpps * kPageH) : mpps * kPageH;
-            RUN(launch_latent_attention(dt, m->lql, m->lqr, pool, l.sink, m->lol, d_seq, d_pos, d_bt, mpps, NT, t_pad, l.heads, l.kv_rank, l.rot_dim,
-                                        l.scale, l.window, max_keys, st));
-            RUN(launch_moe_grouped_gemm(dt, m->lol, l.w_uv, m->lov, d_lat_head, d_lat_n + li, l.heads * tph, l.vdim, l.kv_rank, -1, st));
+            if (latent_attention_tiles_supported(dt, l.kv_rank, l.rot_dim)) {
+                RUN(launch_latent_attention_tiles(dt, m->lql, m->lqr, pool, l.sink, m->lol, d_tiles, n_tiles, d_bt, mpps, t_pad, l.heads, l.kv_rank,
+                                                  l.rot_dim, l.scale, l.window, 0, st));
+                if (l.heads >= kLatentHeadsPerTile)
+                    RUN(launch_latent_attention_tiles(dt, m->lql, m->lqr, pool, l.sink, m->lol, d_stiles, n_short, d_bt, mpps, t_pad, l.heads, l.kv_rank,
+                                                      l.rot_dim, l.scale, l.window, 1, st));
+                else
+                    RUN(launch_latent_attention(dt, m->lql, m->lqr, pool, l.sink, m->lol, d_seq, d_pos, d_bt, mpps, n_short, t_pad, l.heads, l.kv_rank,
+                                                l.rot_dim, l.scale, l.window, max_keys, st, d_short));
+            } else {
+                RUN(launch_latent_attention(dt, m->lql, m->lqr, pool, l.sink, m->lol, d_seq, d_pos, d_bt, mpps, NT, t_pad, l.heads, l.kv_rank, l.rot_dim,
+                                            l.scale, l.window, max_keys, st));
+            }
+            RUN(head_product(m->lol, l.w_uv, m->lov, l.vdim, l.kv_rank));  // out[h] = (sum_j p c_j) . W_uv,h^T
             RUN(launch_latent_gate(dt, m->lov, gate, lp.n_in, m->mix2, NT, t_pad, l.heads, l.vdim, st));
             n_mixed = hv;
         } else {
