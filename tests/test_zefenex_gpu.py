@@ -225,10 +225,10 @@ def test_sixteen_bit_logits_do_not_depend_on_the_schedule(dtype):
 KEY_TOKEN, QUERY_TOKEN = 7, 11
 
 
-def _spiked_model(window, seed):
+def _spiked_model(window, seed, heads=2, dim=16, rot_dim=8, kv_rank=24):
     """One layer whose query projection is bent so that QUERY_TOKEN's query points at KEY_TOKEN's key in every head: where that key is
     visible it takes (nearly) the whole softmax, whatever else the window holds; where it is not, nothing of it shows."""
-    config = ref.make_config([ref.latent_layer(heads=2, dim=16, rot_dim=8, vdim=16, kv_rank=24, window=window, scale=0.25)], softcap=None)
+    config = ref.make_config([ref.latent_layer(heads=heads, dim=dim, rot_dim=rot_dim, vdim=16, kv_rank=kv_rank, window=window, scale=0.25)], softcap=None)
     mx = config["layers"][0]["mixer"]
     if not window:
         del mx["mask"]
@@ -281,6 +281,61 @@ def test_window_edges_with_a_dominant_key(window, query_pos, key_pos, seen, deco
         else:
             got = sess.feed([(r, sequence, [query_pos])]).cpu().numpy()[0]
         assert ref.rel_err(got, expect) < 3e-5
+
+
+# ------------------------------------------------------------------ the tensor-core kernels of 16-bit engines
+EDGES = [(40, 100, 61, True), (40, 100, 60, False), (40, 39, 0, True), (40, 40, 0, False), (64, 127, 64, True), (64, 127, 63, False),
+         (64, 128, 64, False), (64, 128, 65, True), (100, 150, 63, True), (100, 150, 64, True), (300, 299, 0, True), (300, 310, 11, True),
+         (300, 310, 10, False), (1, 50, 49, False), (1, 50, 50, True), (0, 310, 0, True), (70, 200, 131, True), (70, 200, 130, False)]
+
+
+@pytest.mark.parametrize("shape", [dict(heads=2, dim=16, rot_dim=16, kv_rank=32), dict(heads=20, dim=16, rot_dim=16, kv_rank=48),
+                                   dict(heads=3, dim=8, rot_dim=0, kv_rank=256)], ids=["few_heads", "many_heads", "rank_256_no_rotation"])
+@pytest.mark.parametrize("decode", [False, True], ids=["prompt", "decoded"])
+@pytest.mark.parametrize("window,query_pos,key_pos,seen", EDGES, ids=lambda v: str(v))
+def test_tensor_core_attention_edges_with_a_dominant_key(window, query_pos, key_pos, seen, decode, shape):
+    """bfloat16 engines: prompt portions run as tiles of 64 tokens x one head, decoded tokens of many-headed layers as one token x 64 heads
+    (fewer heads: the per-token kernel); a latent rank above 128 is accumulated in blocks of 128 value columns."""
+    config, W, packed = _spiked_model(window, seed=window + 1, **shape)
+    plain = [t for t in tokens_of(config, 3 * (query_pos + 1), query_pos * 1000 + key_pos) if t not in (KEY_TOKEN, QUERY_TOKEN)][:query_pos + 1]
+    with_key, without = list(plain), list(plain)
+    with_key[query_pos] = without[query_pos] = QUERY_TOKEN
+    if key_pos != query_pos:
+        with_key[key_pos] = KEY_TOKEN
+    else:
+        without[query_pos] = plain[query_pos]
+    want, want_without = want_logits(config, W, with_key)[query_pos], want_logits(config, W, without)[query_pos]
+    changed = ref.rel_err(want_without, want)
+    assert changed > 2.5e-2 if seen else changed == 0.0, changed
+    for sequence, expect in ((with_key, want), (without, want_without)):
+        sess = session(config, packed, dtype="bfloat16")
+        r = sess.open()
+        if decode and query_pos > 0:
+            sess.feed([(r, sequence[:query_pos], [])])
+            got = sess.feed([(r, sequence[query_pos:], [0])]).cpu().numpy()[0]
+        else:
+            got = sess.feed([(r, sequence, [query_pos])]).cpu().numpy()[0]
+        assert ref.rel_err(got, expect) < 2e-2, ref.rel_err(got, expect)
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+def test_tensor_core_paths_against_the_oracle_and_against_single_tokens(dtype):
+    """Sizes every tensor-core path takes: tiles of prompt tokens, one-token tiles over 20 heads, a rank of 256 in two value blocks, and --
+    with a prompt of 300 tokens -- the head products on 128-row tiles.  Portions that start in the middle of a page and of a window."""
+    layers = [ref.latent_layer(heads=4, dim=64, rot_dim=32, vdim=80, kv_rank=96, window=40, mlp=ref.dense()),
+              ref.latent_layer(heads=20, dim=64, rot_dim=32, vdim=64, kv_rank=96, window=150, kv_from=0, mlp=ref.moe(experts=2, identity=1, top=3)),
+              ref.latent_layer(heads=2, dim=64, rot_dim=16, vdim=24, kv_rank=256, window=70, scale=0.1)]
+    config = ref.make_config(layers, width=64)
+    W, packed = ref.make_weights(config, seed=41)
+    req = {"a": tokens_of(config, 420, 9)}
+    want = want_logits(config, W, req["a"])
+    tol = 3e-2 if dtype == "bfloat16" else 1e-2
+    runs = {}
+    for name, schedule in (("whole", [[("a", 420)]]), ("cut", [[("a", 300)], [("a", 37)], [("a", 70)], [("a", 3)]] + [[("a", 1)]] * 10)):
+        runs[name] = replay(session(config, packed, dtype=dtype, pool_tokens=448, max_batch_tokens=448), req, schedule)["a"]
+        per_pos = np.linalg.norm(runs[name] - want, axis=-1) / np.linalg.norm(want, axis=-1)
+        assert np.median(per_pos) < tol and per_pos.max() < 5 * tol, (name, float(np.median(per_pos)), float(per_pos.max()))
+    assert ref.rel_err(runs["cut"], runs["whole"]) < tol / 3
 
 
 def test_sink_takes_its_share():
