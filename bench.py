@@ -831,6 +831,174 @@ def run_hybrid(args):
         "e2e": "both numbers are taken through HybridDecoder.forward: host batch description in (one H2D copy per call), device logits out"}), flush=True)
 
 
+LATENT_SIZES = {  # Zefenex-shaped layer lists: four latent-attention layers, the second and fourth reading the first's and third's cached rows;
+    # layer 0 with a dense feed-forward, the others with softmax-routed gated experts, identity experts and a shared expert.  Widths, head counts,
+    # windows and expert counts follow HYBRID_SIZES, so that the attention-only Vasolix-shaped model of the same numbers stands beside it.
+    # The latent rank follows the design's own proportion to the head size (1.5 x dim; 2 x at size l); size x is size m with a rank of 512, four
+    # times the head size, where one CTA no longer holds all value columns and the scores are formed once per block of 128.
+    "s": dict(width=1024, heads=8, dim=128, rot=64, vdim=128, rank=192, window=512, dense_ff=4096, moe=dict(experts=16, identity=2, top=2, ff=512, shared=1024)),
+    "m": dict(width=2048, heads=16, dim=128, rot=64, vdim=128, rank=192, window=1024, dense_ff=8192, moe=dict(experts=32, identity=4, top=4, ff=512, shared=2048)),
+    "l": dict(width=4096, heads=32, dim=128, rot=64, vdim=128, rank=256, window=2048, dense_ff=16384, moe=dict(experts=64, identity=4, top=4, ff=1024, shared=4096)),
+    "x": dict(width=2048, heads=16, dim=128, rot=64, vdim=128, rank=512, window=1024, dense_ff=8192, moe=dict(experts=32, identity=4, top=4, ff=512, shared=2048)),
+}
+
+
+def run_latent(args):
+    """--mode latent: prefill and decode throughput of a Zefenex-shaped model (random weights, bf16) on the layer-list decoder at one of
+    LATENT_SIZES and, in the same process, of the framework's closest other design at equal size: a Vasolix-shaped model of four chunked-
+    attention layers with the same width, head count, window (as its chunk) and expert sizes.  Prefill: one prompt of --prefill-tokens tokens
+    in one engine call.  Decode: --batch sequences with --ctx cached positions each, one token per sequence per step, through the call a
+    served request takes (host batch description in, device logits out)."""
+    import numpy as np
+    import torch
+
+    mod = importlib.import_module("llm-inference-engine_b200")
+    mod.lib()
+    sz = LATENT_SIZES[args.latent_size]
+    W, H, M, V = sz["width"], sz["heads"], sz["moe"], 32000
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    gen = torch.Generator().manual_seed(7)
+
+    def rnd(*shape, std=0.02):
+        return (torch.randn(*shape, generator=gen) * std).to(torch.bfloat16)
+
+    def ones(n):
+        return torch.ones(n, dtype=torch.bfloat16)
+
+    Tq, B, ctx = args.prefill_tokens, args.batch, args.ctx
+    page = mod.KV_PAGE_SIZE
+    per_seq = (max(Tq, ctx + args.steps + args.warmup + 8) + page - 1) // page
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(0, gpu_uuid(dev)) as clocks:
+            e0.record()
+            for _ in range(steps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps, clocks.summary()
+
+    def measure(eng, ids, flops_prefill, bytes_decode):
+        eng.set_pools(per_seq * max(B, 1), max(B, 1))
+        bt = np.arange(per_seq * max(B, 1), dtype=np.int32).reshape(max(B, 1), per_seq)
+        pre_ms, pre_clocks = timed(lambda: eng.forward(ids[:Tq], [0, Tq], [0], [0], bt[:1].reshape(-1), [Tq - 1]), max(3, min(args.steps, 20)), 3)
+        for b in range(B):
+            eng.forward(ids[:ctx], [0, ctx], [0], [b], bt[b:b + 1].reshape(-1), [])
+        state = {"pos": ctx}
+
+        def step():
+            eng.forward(ids[:B], list(range(B + 1)), [state["pos"]] * B, list(range(B)), bt.reshape(-1), list(range(B)))
+            state["pos"] += 1
+
+        dec_ms, dec_clocks = timed(step, args.steps, max(args.warmup, 3))
+        pre_tflops = flops_prefill / (pre_ms * 1e-3) / 1e12
+        dec_gbs = bytes_decode / (dec_ms * 1e-3) / 1e9
+        return {"prefill": {"tokens_per_s": Tq * 1e3 / pre_ms, "ms": pre_ms, "tflops": pre_tflops,
+                            "frac_of_measured_bf16_sustained": pre_tflops / float(peaks.get("bf16_tflops_sustained", 1400.0)), "clocks": pre_clocks},
+                "decode": {"tokens_per_s": B * 1e3 / dec_ms, "ms_per_step": dec_ms, "algorithmic_gb_per_s": dec_gbs,
+                           "frac_of_measured_hbm": dec_gbs / float(peaks.get("hbm_gbs", 6650.0)), "clocks": dec_clocks}}
+
+    ids = torch.randint(0, V, (max(Tq, ctx + 1),), generator=gen).tolist()
+    touched = min(M["experts"], B * M["top"])
+    window = sz["window"]
+    keys_of = lambda pos: min(pos + 1, window)
+    pair_sum = float(sum(keys_of(i) for i in range(Tq)))
+
+    # ---- the Zefenex-shaped model
+    d, dr, dv, r = sz["dim"], sz["rot"], sz["vdim"], sz["rank"]
+    mixer = {"heads": H, "dim": d, "rot_dim": dr, "vdim": dv, "kv_rank": r, "scale": (d + dr) ** -0.5, "mask": {"size": window}, "rot": {"base": 10000.0, "dims": dr}}
+    moe = {"kind": "moe", "expert": {"ff": M["ff"]}, "router": {"experts": M["experts"], "identity": M["identity"], "top": M["top"]}, "shared": {"ff": M["shared"]}}
+    layers = [{"type": "latent_attention", "mixer": dict(mixer), "mlp": {"kind": "dense", "ff": sz["dense_ff"]}},
+              {"type": "latent_attention", "mixer": dict(mixer, kv_from=0), "mlp": moe},
+              {"type": "latent_attention", "mixer": dict(mixer), "mlp": moe},
+              {"type": "latent_attention", "mixer": dict(mixer, kv_from=2), "mlp": moe}]
+    config = {"architecture": "Zefenex", "embedding": {"scale": 1.0}, "layers": layers, "logit_softcap": 30.0, "norm": {"eps": 1e-6}, "vocab": V, "width": W}
+    t = {"embed": rnd(V, W, std=1.0), "head": rnd(V, W)}
+
+    def norm(name):
+        t[name], t[name + ".b"], t[name + ".alpha"] = ones(W), torch.zeros(W, dtype=torch.bfloat16), torch.tensor(0.5, dtype=torch.bfloat16)
+
+    norm("final.norm")
+    lat_params, lat_moe_params, lat_dense_params = 0, 0, 0
+    for i, layer in enumerate(layers):
+        p, mx, ml = f"l{i}.", layer["mixer"], layer["mlp"]
+        for n in ("norm1", "norm1b", "norm2", "norm2b"):
+            norm(p + n)
+        t[p + "ls1"], t[p + "ls2"] = ones(W), ones(W)
+        t.update({p + "mix.q": rnd(H * (d + dr), W), p + "mix.g": rnd(H * dv, W), p + "mix.o": rnd(W, H * dv), p + "mix.uk": rnd(H * d, r, std=0.05),
+                  p + "mix.uv": rnd(H * dv, r, std=0.05), p + "mix.sink": torch.zeros(H, dtype=torch.bfloat16)})
+        lat_params += W * H * (d + dr) + W * H * dv + H * dv * W + H * d * r + H * dv * r
+        if "kv_from" not in mx:
+            t[p + "mix.dkv"], t[p + "mix.dkv.norm"] = rnd(r + dr, W), ones(r)
+            lat_params += W * (r + dr)
+        if ml["kind"] == "dense":
+            t.update({p + "mlp.up": rnd(ml["ff"], W), p + "mlp.up.b": torch.zeros(ml["ff"], dtype=torch.bfloat16), p + "mlp.down": rnd(W, ml["ff"]),
+                      p + "mlp.down.b": torch.zeros(W, dtype=torch.bfloat16)})
+            lat_dense_params += 2 * W * ml["ff"]
+        else:
+            n_out = M["experts"] + M["identity"]
+            t[p + "mlp.router"], t[p + "mlp.correction"] = rnd(n_out, W), torch.zeros(n_out, dtype=torch.bfloat16)
+            gate, up, down = rnd(M["experts"], M["ff"], W), rnd(M["experts"], M["ff"], W), rnd(M["experts"], W, M["ff"])
+            for e in range(M["experts"]):
+                t[f"{p}mlp.e{e}.gate"], t[f"{p}mlp.e{e}.up"], t[f"{p}mlp.e{e}.down"] = gate[e], up[e], down[e]
+            t.update({p + "mlp.shared.gate": rnd(M["shared"], W), p + "mlp.shared.up": rnd(M["shared"], W), p + "mlp.shared.down": rnd(W, M["shared"])})
+            lat_moe_params += 1
+    zef = importlib.import_module("llm-inference-engine_b200.models.zefenex")
+    model = zef.ZefenexModel(config, t, dtype="bfloat16", device=dev, max_tokens=max(Tq, B, 2048), max_seqs=max(B, 1), max_pages_per_seq=per_seq)
+    moe_active = 3 * W * (M["top"] * M["ff"] + M["shared"]) + W * (M["experts"] + M["identity"])
+    lat_active = lat_params + lat_dense_params + lat_moe_params * moe_active
+    lat_attn_flops = 2.0 * len(layers) * H * ((r + dr) + r) * pair_sum
+    lat_w_bytes = 2 * (lat_params + lat_dense_params + lat_moe_params * (3 * W * (touched * M["ff"] + M["shared"]) + W * (M["experts"] + M["identity"]))) + 2 * V * W
+    lat_kv_bytes = 2.0 * len(layers) * B * (r + dr) * keys_of(ctx)   # every layer reads the window's rows once (the heads share them)
+    latent = measure(model.engine, ids, 2.0 * Tq * lat_active + lat_attn_flops, lat_w_bytes + lat_kv_bytes)
+    del model, t
+    torch.cuda.empty_cache()
+
+    # ---- the closest other design at equal size: four chunked-attention layers (values = keys, whole-projection norms), sigmoid-routed experts
+    att = {"type": "attention", "mixer": {"heads": H, "kv_heads": max(1, H // 4), "dim": d, "vdim": d, "scale": d ** -0.5, "mask": {"size": window}},
+           "mlp": {"kind": "moe", "expert": {"ff": M["ff"]}, "router": {"experts": M["experts"], "top": M["top"]}, "shared": {"ff": M["shared"]}}}
+    vconfig = {"architecture": "Vasolix", "layers": [att] * 4, "norm": {"eps": 1e-6}, "vocab": V, "width": W}
+    Gk = att["mixer"]["kv_heads"]
+    t = {"embed": rnd(V, W, std=1.0), "head": rnd(V, W), "final.norm": ones(W)}
+    for i in range(4):
+        p = f"l{i}."
+        t[p + "norm1"], t[p + "norm2"] = ones(W), ones(W)
+        t.update({p + "mix.q": rnd(H * d, W), p + "mix.k": rnd(Gk * d, W), p + "mix.g": rnd(H * d, W), p + "mix.o": rnd(W, H * d),
+                  p + "mix.q.norm": ones(H * d), p + "mix.k.norm": ones(Gk * d), p + "mix.sink": torch.zeros(H, dtype=torch.bfloat16)})
+        t[p + "mlp.router"] = rnd(M["experts"], W)
+        up, down = rnd(M["experts"], M["ff"], W), rnd(M["experts"], W, M["ff"])
+        for e in range(M["experts"]):
+            t[f"{p}mlp.e{e}.up"], t[f"{p}mlp.e{e}.down"] = up[e], down[e]
+        t.update({p + "mlp.shared.up": rnd(M["shared"], W), p + "mlp.shared.down": rnd(W, M["shared"]), p + "mlp.shared.sg": rnd(1, W)})
+    vas = importlib.import_module("llm-inference-engine_b200.models.vasolix")
+    vmodel = vas.VasolixModel(vconfig, t, dtype="bfloat16", device=dev, max_tokens=max(Tq, B, 2048), max_seqs=max(B, 1), max_pages_per_seq=per_seq)
+    v_att = W * (2 * H + Gk) * d + H * d * W
+    v_moe = 2 * W * (M["top"] * M["ff"] + M["shared"]) + W * (M["experts"] + 1)
+    chunk_pairs = float(sum(i % window + 1 for i in range(Tq)))
+    v_flops = 2.0 * Tq * 4 * (v_att + v_moe) + 2.0 * 4 * 2 * H * d * chunk_pairs
+    v_bytes = 2 * 4 * (v_att + 2 * W * (touched * M["ff"] + M["shared"]) + W * (M["experts"] + 1)) + 2 * V * W + 2.0 * 4 * 2 * B * Gk * d * (ctx % window + 1)
+    closest = measure(vmodel.engine, ids, v_flops, v_bytes)
+    print(json.dumps({
+        "metric": "latent-attention model prefill / decode tokens/s", "value": latent["prefill"]["tokens_per_s"], "unit": "tokens/s (prefill)", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "higher_is_better": True, "dtype": "bf16", "data": "synthetic", "impl": "b200",
+        "config": {"model": f"Zefenex-shaped, size {args.latent_size}: width {W}, 4 latent-attention layers ({H} heads, dim {d}+{dr}, rank {r}, window {window}; "
+                            f"layers 1 and 3 read the rows of layers 0 and 2), dense ff {sz['dense_ff']} + 3 x {M['experts']}+{M['identity']} experts top {M['top']}",
+                   "closest": f"Vasolix-shaped: width {W}, 4 chunked-attention layers ({H} heads over {Gk} kv heads, dim {d}, chunk {window}), {M['experts']} experts top {M['top']}",
+                   "prefill_tokens": Tq, "decode_batch": B, "decode_context": ctx, "cache_policy": "weights larger than L2 at sizes m and l; no explicit flush"},
+        "latent": latent, "closest": closest,
+        "e2e": "all numbers are taken through HybridDecoder.forward: host batch description in (one H2D copy per call), device logits out"}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -844,7 +1012,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (debug only: makes the number INVALID)")
     ap.add_argument("--requests", type=int, default=64, help="--mode serve: requests in the stream (prompts of 32..512, 32..256 new tokens)")
     ap.add_argument("--hybrid-size", default="m", choices=list(HYBRID_SIZES), help="--mode hybrid: which Vasolix-shaped model")
-    ap.add_argument("--mode", default="decode", choices=["decode", "prefill", "generate", "serve", "hybrid"],
+    ap.add_argument("--latent-size", default="m", choices=list(LATENT_SIZES), help="--mode latent: which Zefenex-shaped model")
+    ap.add_argument("--mode", default="decode", choices=["decode", "prefill", "generate", "serve", "hybrid", "latent"],
                     help="decode (default, the BASELINE metric); prefill: one pass of --prefill-tokens tokens through all layers; generate: "
                          "the whole loop through b200_generate (prompt of --prefill-tokens tokens, --new-tokens sampled tokens, host in / host out)")
     ap.add_argument("--new-tokens", type=int, default=128)
@@ -873,6 +1042,9 @@ def main():
         return
     if args.mode == "hybrid":
         run_hybrid(args)
+        return
+    if args.mode == "latent":
+        run_latent(args)
         return
     if args.cpu_leg:  # child process of the product arm: the only place of that arm where oracle/ is loaded
         run_cpu_leg(args, cfg)

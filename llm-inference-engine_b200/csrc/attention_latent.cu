@@ -197,8 +197,8 @@ latent_attn_kernel(const T *__restrict__ ql, const T *__restrict__ qr, const T *
 //                 heads share every key row, so the window is read once per 64 heads instead of once per head.
 // A key tile is one page (64 positions) of rows [c | kr]: it arrives by cp.async into a two-stage ring, S = Q K^T over all kv_rank +
 // rot_dim columns and O += P V over value columns [v0, v0 + 16 NV) OF THE SAME TILE run on mma.sync.m16n8k16 with fp32 accumulators, the
-// softmax is the online form in fp32.  blockIdx.z selects a block of 128 value columns when kv_rank > 128 (the scores are formed again
-// per block).  The sink enters as the INITIAL running state (max = sink, sum = 1, nothing accumulated): a key with that logit and a
+// softmax is the online form in fp32.  A CTA accumulates the whole rank up to 256 value columns; above that blockIdx.z selects a block of
+// 128 value columns (the scores are formed again per block).  The sink enters as the INITIAL running state (max = sink, sum = 1, nothing accumulated): a key with that logit and a
 // zero value.  The mask is evaluated per element: a tile of queries may straddle a window edge; the key tiles walked run from the
 // window start of the tile's first query to its last query.  Rows of a key tile past the tile's last query are zeroed, not fetched:
 // they may belong to a page's previous owner, and 0 x NaN is NaN on the tensor core.
@@ -253,7 +253,7 @@ latent_attn_mma_kernel(const T *__restrict__ ql, const T *__restrict__ qr, const
     const int row0 = tile.y, pos0 = tile.w;
     const int h0 = by_head ? blockIdx.y * kLatTileQ : blockIdx.y;
     const int nrows = by_head ? min(kLatTileQ, heads - h0) : tile.z;
-    const int v0 = blockIdx.z * 128;
+    const int v0 = blockIdx.z * (16 * NV);
     const int *bt = block_table + (size_t)tile.x * mpps;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
     const int last = by_head ? pos0 : pos0 + nrows - 1;
@@ -424,10 +424,17 @@ int launch_latent_attention(int dtype, const void *ql, const void *qr, const voi
     return cuda_status("latent_attention launch");
 }
 
+// value blocks of 16 columns one CTA accumulates for this rank: the whole rank up to 256 columns (fp32 accumulators in registers), blocks of
+// 128 (eight each, blockIdx.z of them) for larger ranks that are multiples of 128; 0: no tensor-core form
+static int latent_value_blocks(int kv_rank) {
+    if (kv_rank % 16 != 0) return 0;
+    if (kv_rank <= 128 || (kv_rank <= 256 && kv_rank % 32 == 0)) return kv_rank / 16;
+    return kv_rank % 128 == 0 ? 8 : 0;
+}
+
 bool latent_attention_tiles_supported(int dtype, int kv_rank, int rot_dim) {
     const int ld = (kv_rank + rot_dim + 63) / 64 * 64;
-    return dtype != B200_F32 && kv_rank % 16 == 0 && rot_dim % 16 == 0 && (kv_rank <= 128 || kv_rank % 128 == 0) &&
-           (size_t)3 * kLatTileQ * ld * 2 <= 227 * 1024;
+    return dtype != B200_F32 && rot_dim % 16 == 0 && latent_value_blocks(kv_rank) > 0 && (size_t)3 * kLatTileQ * ld * 2 <= 227 * 1024;
 }
 
 template <typename T, int NV>
@@ -447,27 +454,27 @@ int launch_latent_attention_tiles(int dtype, const void *ql, const void *qr, con
                                   int window, int by_head, cudaStream_t st) {
     if (n_tiles == 0) return B200_OK;
     if (!latent_attention_tiles_supported(dtype, kv_rank, rot_dim)) {
-        set_error("latent_attention tiles: 16-bit dtypes, kv_rank and rot_dim multiples of 16, kv_rank <= 128 or a multiple of 128");
+        set_error("latent_attention tiles: 16-bit dtypes, kv_rank and rot_dim multiples of 16, kv_rank <= 128, a multiple of 32 up to 256, or a multiple of 128");
         return B200_ERR_UNSUPPORTED;
     }
-    const dim3 grid(n_tiles, by_head ? (heads + kLatTileQ - 1) / kLatTileQ : heads, kv_rank > 128 ? kv_rank / 128 : 1);
-    const int nv = kv_rank > 128 ? 8 : kv_rank / 16;
-#define B200_LAT_TILES(TT)                                                                                                                       \
-    switch (nv) {                                                                                                                                \
-        case 1: return launch_latent_mma_t<TT, 1>(ql, qr, pool, sink, ol, tiles, grid, block_table, mpps, t_pad, heads, kv_rank, rot_dim, scale, window, by_head, st); \
-        case 2: return launch_latent_mma_t<TT, 2>(ql, qr, pool, sink, ol, tiles, grid, block_table, mpps, t_pad, heads, kv_rank, rot_dim, scale, window, by_head, st); \
-        case 3: return launch_latent_mma_t<TT, 3>(ql, qr, pool, sink, ol, tiles, grid, block_table, mpps, t_pad, heads, kv_rank, rot_dim, scale, window, by_head, st); \
-        case 4: return launch_latent_mma_t<TT, 4>(ql, qr, pool, sink, ol, tiles, grid, block_table, mpps, t_pad, heads, kv_rank, rot_dim, scale, window, by_head, st); \
-        case 5: return launch_latent_mma_t<TT, 5>(ql, qr, pool, sink, ol, tiles, grid, block_table, mpps, t_pad, heads, kv_rank, rot_dim, scale, window, by_head, st); \
-        case 6: return launch_latent_mma_t<TT, 6>(ql, qr, pool, sink, ol, tiles, grid, block_table, mpps, t_pad, heads, kv_rank, rot_dim, scale, window, by_head, st); \
-        case 7: return launch_latent_mma_t<TT, 7>(ql, qr, pool, sink, ol, tiles, grid, block_table, mpps, t_pad, heads, kv_rank, rot_dim, scale, window, by_head, st); \
-        default: return launch_latent_mma_t<TT, 8>(ql, qr, pool, sink, ol, tiles, grid, block_table, mpps, t_pad, heads, kv_rank, rot_dim, scale, window, by_head, st); \
+    const int nv = latent_value_blocks(kv_rank);
+    const dim3 grid(n_tiles, by_head ? (heads + kLatTileQ - 1) / kLatTileQ : heads, kv_rank / (16 * nv));
+#define B200_LAT_CASE(TT, N) \
+    case N: return launch_latent_mma_t<TT, N>(ql, qr, pool, sink, ol, tiles, grid, block_table, mpps, t_pad, heads, kv_rank, rot_dim, scale, window, by_head, st);
+#define B200_LAT_TILES(TT)                                                                                                              \
+    switch (nv) {                                                                                                                       \
+        B200_LAT_CASE(TT, 1) B200_LAT_CASE(TT, 2) B200_LAT_CASE(TT, 3) B200_LAT_CASE(TT, 4) B200_LAT_CASE(TT, 5) B200_LAT_CASE(TT, 6)    \
+        B200_LAT_CASE(TT, 7) B200_LAT_CASE(TT, 8) B200_LAT_CASE(TT, 10) B200_LAT_CASE(TT, 12) B200_LAT_CASE(TT, 14) B200_LAT_CASE(TT, 16) \
+        default: break;                                                                                                                 \
     }
     if (dtype == B200_BF16) {
         B200_LAT_TILES(__nv_bfloat16)
     }
     B200_LAT_TILES(__half)
 #undef B200_LAT_TILES
+#undef B200_LAT_CASE
+    set_error("latent_attention tiles: no kernel for rank %d", kv_rank);
+    return B200_ERR_UNSUPPORTED;
 }
 
 int launch_latent_gate(int dtype, const void *ov, const void *gate_in, int gate_ld, void *out, int tokens, int t_pad, int heads, int vdim,

@@ -148,25 +148,47 @@ sublayer_residual_kernel(float *__restrict__ x, const T *__restrict__ y_dense, c
                          int has_y) {
     extern __shared__ __align__(16) float ys[];  // [width]
     __shared__ float red[33];
+    constexpr int V = Elem<T>::kVec;
     const int t = blockIdx.x;
+    // 16-byte pieces when every row starts on a 16-byte boundary (the sums are formed in the same order as element by element)
+    const bool vec = width % V == 0 && ((reinterpret_cast<size_t>(x) | reinterpret_cast<size_t>(y_dense) | reinterpret_cast<size_t>(y_rows) |
+                                         reinterpret_cast<size_t>(y_shared) | reinterpret_cast<size_t>(h_in) | reinterpret_cast<size_t>(h_out) |
+                                         reinterpret_cast<size_t>(trace)) & 15) == 0;
+    const int step = vec ? V : 1;
     float inv = 1.0f;
     if (has_y) {
         float ss = 0.0f;
-        for (int c = threadIdx.x; c < width; c += blockDim.x) {
-            float v;
+        const float sg = (!y_dense && y_shared) ? (shared_gate ? shared_gate[t] : 1.0f) : 0.0f;
+        for (int c = threadIdx.x * step; c < width; c += blockDim.x * step) {
+            float v[V];
             if (y_dense) {
-                v = Elem<T>::to_f(y_dense[(size_t)t * width + c]) + (y_bias ? y_bias[c] : 0.0f);
+                if (vec) unpack16<T>(ld_v4(y_dense + (size_t)t * width + c), v);
+                else v[0] = Elem<T>::to_f(y_dense[(size_t)t * width + c]);
+                if (y_bias)
+                    for (int i = 0; i < step; ++i) v[i] += y_bias[c + i];
             } else {
-                v = 0.0f;
+#pragma unroll
+                for (int i = 0; i < V; ++i) v[i] = 0.0f;
                 for (int k = 0; k < top; ++k) {
                     const int r = pair_row[(size_t)t * top + k];
                     const float w = pair_weight ? pair_weight[(size_t)t * top + k] : 1.0f;
-                    v = fmaf(w, Elem<T>::to_f(r >= 0 ? y_rows[(size_t)r * width + c] : h_in[(size_t)t * width + c]), v);
+                    const T *src = r >= 0 ? y_rows + (size_t)r * width + c : h_in + (size_t)t * width + c;
+                    float f[V];
+                    if (vec) unpack16<T>(ld_v4(src), f);
+                    else f[0] = Elem<T>::to_f(src[0]);
+                    for (int i = 0; i < step; ++i) v[i] = fmaf(w, f[i], v[i]);
                 }
-                if (y_shared) v = fmaf(shared_gate ? shared_gate[t] : 1.0f, Elem<T>::to_f(y_shared[(size_t)t * width + c]), v);
+                if (y_shared) {
+                    float f[V];
+                    if (vec) unpack16<T>(ld_v4(y_shared + (size_t)t * width + c), f);
+                    else f[0] = Elem<T>::to_f(y_shared[(size_t)t * width + c]);
+                    for (int i = 0; i < step; ++i) v[i] = fmaf(sg, f[i], v[i]);
+                }
             }
-            ys[c] = v;
-            ss = fmaf(v, v, ss);
+            for (int i = 0; i < step; ++i) {
+                ys[c + i] = v[i];
+                ss = fmaf(v[i], v[i], ss);
+            }
         }
         if (norm == B200_NORM_RMS_POST) {
             ss = block_sum(ss, red);
@@ -174,16 +196,42 @@ sublayer_residual_kernel(float *__restrict__ x, const T *__restrict__ y_dense, c
         }
     }
     const float a_post = (has_y && norm == B200_NORM_DYT_PRE_POST) ? post[2 * width] : 0.0f, a_pre = pre ? pre[2 * width] : 0.0f;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {  // a thread reads back the elements of ys it wrote
-        float v = x[(size_t)t * width + c];
-        if (has_y) {
-            float n = norm == B200_NORM_RMS_POST ? ys[c] * inv * post[c] : dyt_apply(post, width, c, a_post, ys[c]);
-            if (ls) n *= ls[c];
-            v += n;
-            x[(size_t)t * width + c] = v;
+    for (int c = threadIdx.x * step; c < width; c += blockDim.x * step) {  // a thread reads back the elements of ys it wrote
+        float v[V];
+        if (vec) {
+#pragma unroll
+            for (int i = 0; i < V; i += 4) {
+                const float4 xv = *reinterpret_cast<const float4 *>(x + (size_t)t * width + c + i);
+                v[i] = xv.x, v[i + 1] = xv.y, v[i + 2] = xv.z, v[i + 3] = xv.w;
+            }
+        } else {
+            v[0] = x[(size_t)t * width + c];
         }
-        if (trace) trace[(size_t)t * width + c] = v;
-        if (h_out) h_out[(size_t)t * width + c] = Elem<T>::from_f(pre ? dyt_apply(pre, width, c, a_pre, v) : v);
+        if (has_y) {
+            for (int i = 0; i < step; ++i) {
+                float n = norm == B200_NORM_RMS_POST ? ys[c + i] * inv * post[c + i] : dyt_apply(post, width, c + i, a_post, ys[c + i]);
+                if (ls) n *= ls[c + i];
+                v[i] += n;
+            }
+        }
+        if (vec) {
+#pragma unroll
+            for (int i = 0; i < V; i += 4) {
+                const float4 r = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                if (has_y) *reinterpret_cast<float4 *>(x + (size_t)t * width + c + i) = r;
+                if (trace) *reinterpret_cast<float4 *>(trace + (size_t)t * width + c + i) = r;
+            }
+            if (h_out) {
+                if (pre)
+#pragma unroll
+                    for (int i = 0; i < V; ++i) v[i] = dyt_apply(pre, width, c + i, a_pre, v[i]);
+                st_v4(h_out + (size_t)t * width + c, pack16<T>(v));
+            }
+        } else {
+            if (has_y) x[(size_t)t * width + c] = v[0];
+            if (trace) trace[(size_t)t * width + c] = v[0];
+            if (h_out) h_out[(size_t)t * width + c] = Elem<T>::from_f(pre ? dyt_apply(pre, width, c, a_pre, v[0]) : v[0]);
+        }
     }
 }
 
@@ -766,7 +814,9 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
             if (latent_attention_tiles_supported(dt, l.kv_rank, l.rot_dim)) {
                 RUN(launch_latent_attention_tiles(dt, m->lql, m->lqr, pool, l.sink, m->lol, d_tiles, n_tiles, d_bt, mpps, t_pad, l.heads, l.kv_rank,
                                                   l.rot_dim, l.scale, l.window, 0, st));
-                if (l.heads >= kLatentHeadsPerTile)
+                // decoded tokens: one tile per token over its heads reads the window once per 64 heads, but is one CTA per token; the per-token
+                // kernel is one CTA per (token, head).  The tile form pays once its CTAs fill half the device.
+                if (l.heads >= kLatentHeadsPerTile && n_short * ((l.heads + 63) / 64) >= 74)
                     RUN(launch_latent_attention_tiles(dt, m->lql, m->lqr, pool, l.sink, m->lol, d_stiles, n_short, d_bt, mpps, t_pad, l.heads, l.kv_rank,
                                                       l.rot_dim, l.scale, l.window, 1, st));
                 else

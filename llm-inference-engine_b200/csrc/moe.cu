@@ -172,11 +172,27 @@ moe_gather_rows_kernel(const T *__restrict__ h, const int *__restrict__ row_toke
     for (int c = threadIdx.x; c < width; c += blockDim.x) xg[(size_t)r * width + c] = t >= 0 ? h[(size_t)t * width + c] : Elem<T>::from_f(0.0f);
 }
 
-// out[r, c] = act(in[r, c]) * in[r, inner + c] for rows r < *n_rows_live (all `rows` when n_tiles is NULL); in [rows, 2 * inner]
+// out[r, c] = act(in[r, c]) * in[r, inner + c] for rows r < *n_tiles * tile (all `rows` when n_tiles is NULL); in [rows, 2 * inner].
+// One 16-byte piece of the output per thread when the rows start on 16-byte boundaries, else one element.
 template <typename T>
 __global__ void gated_activation_kernel(const T *__restrict__ in, T *__restrict__ out, int rows, int inner, int act, const int *__restrict__ n_tiles,
                                         int tile) {
+    constexpr int V = Elem<T>::kVec;
     const int live = n_tiles ? min(rows, *n_tiles * tile) : rows;
+    if (inner % V == 0 && ((reinterpret_cast<size_t>(in) | reinterpret_cast<size_t>(out)) & 15) == 0) {
+        const int per_row = inner / V;
+        const size_t n = (size_t)live * per_row;
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+            const size_t r = i / per_row, c = (i - r * per_row) * V;
+            float g[V], u[V];
+            unpack16<T>(ld_v4(in + r * 2 * inner + c), g);
+            unpack16<T>(ld_v4(in + r * 2 * inner + inner + c), u);
+#pragma unroll
+            for (int e = 0; e < V; ++e) g[e] = act_apply(g[e], act) * u[e];
+            st_v4(out + r * inner + c, pack16<T>(g));
+        }
+        return;
+    }
     const size_t n = (size_t)live * inner;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         const size_t r = i / inner, c = i - r * inner;
@@ -185,9 +201,26 @@ __global__ void gated_activation_kernel(const T *__restrict__ in, T *__restrict_
     }
 }
 
-// in place: x[r, c] = act(x[r, c] + bias[c]) (bias may be NULL, act < 0: none)
+// in place: x[r, c] = act(x[r, c] + bias[c]) (bias may be NULL, act < 0: none); 16-byte pieces when the rows start on 16-byte boundaries
 template <typename T>
 __global__ void bias_activation_kernel(T *__restrict__ x, const float *__restrict__ bias, size_t rows, int cols, int act) {
+    constexpr int V = Elem<T>::kVec;
+    if (cols % V == 0 && (reinterpret_cast<size_t>(x) & 15) == 0) {
+        const int per_row = cols / V;
+        const size_t n = rows * per_row;
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+            const int c = (int)(i % per_row) * V;
+            float f[V];
+            unpack16<T>(ld_v4(x + i * V), f);
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+                const float v = f[e] + (bias ? bias[c + e] : 0.0f);
+                f[e] = act >= 0 ? act_apply(v, act) : v;
+            }
+            st_v4(x + i * V, pack16<T>(f));
+        }
+        return;
+    }
     const size_t n = rows * cols;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         float v = Elem<T>::to_f(x[i]);
@@ -394,16 +427,16 @@ int launch_moe_gather_rows(int dtype, const void *h, const int *row_token, void 
 
 int launch_gated_activation(int dtype, const void *in, void *out, int rows, int inner, int act, const int *n_tiles, int tile, cudaStream_t st) {
     if (rows == 0 || inner == 0) return B200_OK;
-    const size_t n = (size_t)rows * inner;
-    const unsigned grid = (unsigned)std::min<size_t>((n + 255) / 256, 148 * 16);
+    const size_t n = (size_t)rows * inner / 4;
+    const unsigned grid = (unsigned)std::max<size_t>(1, std::min<size_t>((n + 255) / 256, 148 * 16));
     B200_DISPATCH_DTYPE(dtype, { gated_activation_kernel<T><<<grid, 256, 0, st>>>((const T *)in, (T *)out, rows, inner, act, n_tiles, tile); });
     return cuda_status("gated_activation launch");
 }
 
 int launch_bias_activation(int dtype, void *x, const float *bias, size_t rows, int cols, int act, cudaStream_t st) {
     if (rows == 0 || cols == 0) return B200_OK;
-    const size_t n = rows * cols;
-    const unsigned grid = (unsigned)std::min<size_t>((n + 255) / 256, 148 * 16);
+    const size_t n = rows * cols / 4;
+    const unsigned grid = (unsigned)std::max<size_t>(1, std::min<size_t>((n + 255) / 256, 148 * 16));
     B200_DISPATCH_DTYPE(dtype, { bias_activation_kernel<T><<<grid, 256, 0, st>>>((T *)x, bias, rows, cols, act); });
     return cuda_status("bias_activation launch");
 }
