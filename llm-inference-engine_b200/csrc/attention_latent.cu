@@ -52,11 +52,25 @@ latent_prep_kernel(const T *__restrict__ proj, int ld, int q_col, int kv_col, T 
         return self;
     };
     const int per = dim + rot_dim;
-    for (int idx = threadIdx.x; idx < heads * per; idx += blockDim.x) {
-        const int h = idx / per, c = idx - h * per;
-        const T *qh = row + q_col + (size_t)h * per;
-        if (c < dim) qn[((size_t)h * t_pad + t) * dim + c] = qh[c];
-        else qr[((size_t)t * heads + h) * rot_dim + (c - dim)] = Elem<T>::from_f(rotated(qh + dim, c - dim));
+    constexpr int V = Elem<T>::kVec;
+    if (dim % V == 0 && rot_dim % V == 0 && ld % V == 0 && q_col % V == 0 &&
+        ((reinterpret_cast<size_t>(proj) | reinterpret_cast<size_t>(qn)) & 15) == 0) {  // the un-rotated part moves in 16-byte pieces
+        const int pieces = dim / V;
+        for (int idx = threadIdx.x; idx < heads * pieces; idx += blockDim.x) {
+            const int h = idx / pieces, c = (idx - h * pieces) * V;
+            st_v4(qn + ((size_t)h * t_pad + t) * dim + c, ld_v4(row + q_col + (size_t)h * per + c));
+        }
+        for (int idx = threadIdx.x; idx < heads * rot_dim; idx += blockDim.x) {
+            const int h = idx / rot_dim, r = idx - h * rot_dim;
+            qr[((size_t)t * heads + h) * rot_dim + r] = Elem<T>::from_f(rotated(row + q_col + (size_t)h * per + dim, r));
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < heads * per; idx += blockDim.x) {
+            const int h = idx / per, c = idx - h * per;
+            const T *qh = row + q_col + (size_t)h * per;
+            if (c < dim) qn[((size_t)h * t_pad + t) * dim + c] = qh[c];
+            else qr[((size_t)t * heads + h) * rot_dim + (c - dim)] = Elem<T>::from_f(rotated(qh + dim, c - dim));
+        }
     }
     if (kv_col < 0) return;  // this layer reads another layer's rows
     const T *kv = row + kv_col;
@@ -202,6 +216,8 @@ latent_attn_kernel(const T *__restrict__ ql, const T *__restrict__ qr, const T *
 // zero value.  The mask is evaluated per element: a tile of queries may straddle a window edge; the key tiles walked run from the
 // window start of the tile's first query to its last query.  Rows of a key tile past the tile's last query are zeroed, not fetched:
 // they may belong to a page's previous owner, and 0 x NaN is NaN on the tensor core.
+// One-token tiles that would leave most of the device idle share out their key tiles over `splits` CTAs (blockIdx.z % splits), which write
+// un-normalised sums and their running state to `part`; latent_combine_kernel joins them.  The sink belongs to share 0.
 // tiles: int4 per tile {sequence, first packed row, rows (1..64; by_head: unused), position of the first row}.
 namespace {
 __device__ __forceinline__ void lat_cp_async16(void *smem, const void *gmem) {
@@ -238,13 +254,14 @@ template <> __device__ __forceinline__ unsigned lat_pack2<__half>(float lo, floa
 // eight pieces: conflict-free ldmatrix
 __device__ __forceinline__ int lat_swz(int row, int col, int ld) { return row * ld + ((((col >> 3) ^ (row & 7)) << 3) | (col & 7)); }
 constexpr int kLatTileQ = 64;
+constexpr int kLatentFillCtas = 148;
 }  // namespace
 
 template <typename T, int NV>
 __global__ void __launch_bounds__(128)
 latent_attn_mma_kernel(const T *__restrict__ ql, const T *__restrict__ qr, const T *__restrict__ pool, const float *__restrict__ sink,
                        T *__restrict__ ol, const int4 *__restrict__ tiles, const int *__restrict__ block_table, int mpps, int t_pad, int heads,
-                       int kv_rank, int rot_dim, int ld, float scale, int window, int by_head) {
+                       int kv_rank, int rot_dim, int ld, float scale, int window, int by_head, int splits, float *__restrict__ part) {
     extern __shared__ __align__(16) unsigned char smraw[];
     T *qs = reinterpret_cast<T *>(smraw);  // [64][ld]
     T *ks = qs + kLatTileQ * ld;           // [2][64][ld]
@@ -253,12 +270,18 @@ latent_attn_mma_kernel(const T *__restrict__ ql, const T *__restrict__ qr, const
     const int row0 = tile.y, pos0 = tile.w;
     const int h0 = by_head ? blockIdx.y * kLatTileQ : blockIdx.y;
     const int nrows = by_head ? min(kLatTileQ, heads - h0) : tile.z;
-    const int v0 = blockIdx.z * (16 * NV);
+    const int sp = blockIdx.z % splits;  // which share of the key tiles this CTA walks (splits > 1: partial results go to `part`)
+    const int v0 = (blockIdx.z / splits) * (16 * NV);
     const int *bt = block_table + (size_t)tile.x * mpps;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
     const int last = by_head ? pos0 : pos0 + nrows - 1;
     const int first = window > 0 ? max(0, pos0 - window + 1) : 0;
-    const int tile_lo = first / kPageL, tile_hi = last / kPageL;
+    int tile_lo = first / kPageL, tile_hi = last / kPageL;
+    if (splits > 1) {
+        const int per = (tile_hi - tile_lo + splits) / splits;
+        tile_lo += sp * per;
+        tile_hi = min(tile_hi, tile_lo + per - 1);  // may leave no tile: this CTA then reports an empty share
+    }
 
     auto load_kv = [&](int kt, int stage) {
         const T *src = pool + (size_t)bt[kt] * kPageL * dk;
@@ -269,7 +292,7 @@ latent_attn_mma_kernel(const T *__restrict__ ql, const T *__restrict__ qr, const
             else *reinterpret_cast<uint4 *>(dst + lat_swz(r, c, ld)) = make_uint4(0, 0, 0, 0);
         }
     };
-    load_kv(tile_lo, 0);
+    if (tile_lo <= tile_hi) load_kv(tile_lo, 0);
     asm volatile("cp.async.commit_group;" ::: "memory");
     for (int i = threadIdx.x; i < kLatTileQ * pieces; i += 128) {
         const int r = i / pieces, c = (i - r * pieces) * 8;
@@ -288,7 +311,7 @@ latent_attn_mma_kernel(const T *__restrict__ ql, const T *__restrict__ qr, const
     const int p_a = by_head ? pos0 : pos0 + r_a, p_b = by_head ? pos0 : pos0 + r_b;
     const int lo_a = window > 0 ? p_a - window : -1, lo_b = window > 0 ? p_b - window : -1;  // visible keys: lo < key <= p
     float m_a, m_b, l_a, l_b;
-    if (sink) {
+    if (sink && sp == 0) {
         m_a = sink[by_head ? min(h0 + r_a, heads - 1) : h0] * kLog2e, m_b = sink[by_head ? min(h0 + r_b, heads - 1) : h0] * kLog2e;
         l_a = l_b = tig == 0 ? 1.0f : 0.0f;  // the sum is kept per lane and joined at the end
     } else {
@@ -305,6 +328,10 @@ latent_attn_mma_kernel(const T *__restrict__ ql, const T *__restrict__ qr, const
         asm volatile("cp.async.wait_group 1;" ::: "memory");
         __syncthreads();
         const T *kst = ks + stage * kPageL * ld;
+        if (warp * 16 >= nrows) {  // a warp without live rows only keeps the ring's barriers
+            __syncthreads();
+            continue;
+        }
         float s[8][4];
 #pragma unroll
         for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
@@ -367,6 +394,24 @@ latent_attn_mma_kernel(const T *__restrict__ ql, const T *__restrict__ qr, const
     l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
     l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
     l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+    if (part) {
+        // a share of the keys: the un-normalised sums and the running state (max in log2 units, sum), fp32, per (tile, share, row):
+        // [kv_rank sums | max | sum]; latent_combine_kernel joins the shares
+        const size_t stride = (size_t)kv_rank + 2;
+        float *pa = part + (((size_t)blockIdx.x * splits + sp) * heads + (by_head ? h0 + r_a : h0)) * stride;
+        float *pb = part + (((size_t)blockIdx.x * splits + sp) * heads + (by_head ? h0 + r_b : h0)) * stride;
+#pragma unroll
+        for (int j = 0; j < 2 * NV; ++j) {
+            const int c = v0 + j * 8 + tig * 2;
+            if (r_a < nrows) pa[c] = o[j][0], pa[c + 1] = o[j][1];
+            if (r_b < nrows) pb[c] = o[j][2], pb[c + 1] = o[j][3];
+        }
+        if (v0 == 0 && tig == 0) {
+            if (r_a < nrows) pa[kv_rank] = m_a, pa[kv_rank + 1] = l_a;
+            if (r_b < nrows) pb[kv_rank] = m_b, pb[kv_rank + 1] = l_b;
+        }
+        return;
+    }
     const float i_a = 1.0f / l_a, i_b = 1.0f / l_b;
     T *out_a = ol + (by_head ? ((size_t)(h0 + r_a) * t_pad + row0) : ((size_t)h0 * t_pad + row0 + r_a)) * kv_rank + v0;
     T *out_b = ol + (by_head ? ((size_t)(h0 + r_b) * t_pad + row0) : ((size_t)h0 * t_pad + row0 + r_b)) * kv_rank + v0;
@@ -375,6 +420,25 @@ latent_attn_mma_kernel(const T *__restrict__ ql, const T *__restrict__ qr, const
         const int c = j * 8 + tig * 2;
         if (r_a < nrows) *reinterpret_cast<unsigned *>(out_a + c) = lat_pack2<T>(o[j][0] * i_a, o[j][1] * i_a);
         if (r_b < nrows) *reinterpret_cast<unsigned *>(out_b + c) = lat_pack2<T>(o[j][2] * i_b, o[j][3] * i_b);
+    }
+}
+
+// joins the shares of one-token tiles: grid (tiles, heads)
+template <typename T>
+__global__ void __launch_bounds__(128)
+latent_combine_kernel(const float *__restrict__ part, const int4 *__restrict__ tiles, T *__restrict__ ol, int t_pad, int heads, int kv_rank, int splits) {
+    const int h = blockIdx.y, t = tiles[blockIdx.x].y;
+    const size_t stride = (size_t)kv_rank + 2;
+    const float *p0 = part + ((size_t)blockIdx.x * splits * heads + h) * stride;
+    float mx = -INFINITY;
+    for (int s = 0; s < splits; ++s) mx = fmaxf(mx, p0[(size_t)s * heads * stride + kv_rank]);
+    float den = 0.0f;
+    for (int s = 0; s < splits; ++s) den += p0[(size_t)s * heads * stride + kv_rank + 1] * exp2f(p0[(size_t)s * heads * stride + kv_rank] - mx);
+    const float inv = 1.0f / den;
+    for (int c = threadIdx.x; c < kv_rank; c += blockDim.x) {
+        float a = 0.0f;
+        for (int s = 0; s < splits; ++s) a = fmaf(p0[(size_t)s * heads * stride + c], exp2f(p0[(size_t)s * heads * stride + kv_rank] - mx), a);
+        ol[((size_t)h * t_pad + t) * kv_rank + c] = Elem<T>::from_f(a * inv);
     }
 }
 
@@ -440,27 +504,39 @@ bool latent_attention_tiles_supported(int dtype, int kv_rank, int rot_dim) {
 template <typename T, int NV>
 static int launch_latent_mma_t(const void *ql, const void *qr, const void *pool, const float *sink, void *ol, const int *tiles, dim3 grid,
                                const int *block_table, int mpps, int t_pad, int heads, int kv_rank, int rot_dim, float scale, int window, int by_head,
-                               cudaStream_t st) {
+                               int splits, float *part, cudaStream_t st) {
     const int ld = (kv_rank + rot_dim + 63) / 64 * 64;
     const size_t smem = (size_t)3 * kLatTileQ * ld * sizeof(T);
     cudaFuncSetAttribute(latent_attn_mma_kernel<T, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     latent_attn_mma_kernel<T, NV><<<grid, 128, smem, st>>>((const T *)ql, (const T *)qr, (const T *)pool, sink, (T *)ol, (const int4 *)tiles,
-                                                           block_table, mpps, t_pad, heads, kv_rank, rot_dim, ld, scale, window, by_head);
+                                                           block_table, mpps, t_pad, heads, kv_rank, rot_dim, ld, scale, window, by_head, splits,
+                                                           splits > 1 ? part : nullptr);
+    if (splits > 1)
+        latent_combine_kernel<T><<<dim3(grid.x, heads), 128, 0, st>>>(part, (const int4 *)tiles, (T *)ol, t_pad, heads, kv_rank, splits);
     return cuda_status("latent_attention (tensor core) launch");
 }
 
 int launch_latent_attention_tiles(int dtype, const void *ql, const void *qr, const void *pool, const float *sink, void *ol, const int *tiles,
                                   int n_tiles, const int *block_table, int mpps, int t_pad, int heads, int kv_rank, int rot_dim, float scale,
-                                  int window, int by_head, cudaStream_t st) {
+                                  int window, int by_head, float *part, int part_tiles, cudaStream_t st) {
     if (n_tiles == 0) return B200_OK;
     if (!latent_attention_tiles_supported(dtype, kv_rank, rot_dim)) {
         set_error("latent_attention tiles: 16-bit dtypes, kv_rank and rot_dim multiples of 16, kv_rank <= 128, a multiple of 32 up to 256, or a multiple of 128");
         return B200_ERR_UNSUPPORTED;
     }
     const int nv = latent_value_blocks(kv_rank);
-    const dim3 grid(n_tiles, by_head ? (heads + kLatTileQ - 1) / kLatTileQ : heads, kv_rank / (16 * nv));
+    dim3 grid(n_tiles, by_head ? (heads + kLatTileQ - 1) / kLatTileQ : heads, kv_rank / (16 * nv));
+    // one-token tiles that do not fill the device: the key tiles of every token are shared out over up to 8 CTAs, whose partial results
+    // (part: fp32 [part_tiles, heads, kv_rank + 2]) a second kernel joins
+    int splits = 1;
+    if (by_head && part) {
+        const int ctas = (int)(grid.x * grid.y * grid.z);
+        if (ctas < kLatentFillCtas) splits = std::min(8, std::min(kLatentFillCtas / ctas, part_tiles / n_tiles));
+        if (splits < 1) splits = 1;
+    }
+    grid.z *= splits;
 #define B200_LAT_CASE(TT, N) \
-    case N: return launch_latent_mma_t<TT, N>(ql, qr, pool, sink, ol, tiles, grid, block_table, mpps, t_pad, heads, kv_rank, rot_dim, scale, window, by_head, st);
+    case N: return launch_latent_mma_t<TT, N>(ql, qr, pool, sink, ol, tiles, grid, block_table, mpps, t_pad, heads, kv_rank, rot_dim, scale, window, by_head, splits, part, st);
 #define B200_LAT_TILES(TT)                                                                                                              \
     switch (nv) {                                                                                                                       \
         B200_LAT_CASE(TT, 1) B200_LAT_CASE(TT, 2) B200_LAT_CASE(TT, 3) B200_LAT_CASE(TT, 4) B200_LAT_CASE(TT, 5) B200_LAT_CASE(TT, 6)    \

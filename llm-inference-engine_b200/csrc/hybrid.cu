@@ -27,6 +27,7 @@
 namespace b200 {
 
 constexpr int kPageH = B200_KV_PAGE_SIZE;
+constexpr int kLatentPartTiles = 1184;     // (one-token tile, key share) pairs the partial-result scratch of the latent attention holds: 148 x 8
 constexpr int kLatentHeadsPerTile = 16;  // latent layers with at least this many heads run a decoded token's heads as one tensor-core tile
 static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
@@ -139,7 +140,7 @@ __device__ __forceinline__ float dyt_apply(const float *__restrict__ p, int widt
 //   x[t, :] += ls * norm(y[t, :])    norm = RMS (post = g) or Dynamic Tanh (post packed);   has_y == 0: x stays as it is;
 //   h_out[t, :] = T(pre ? dyt(x[t, :]; pre) : x[t, :]): what the next sublayer's projections read.
 // h_in and h_out may be the same buffer: an element is read by the thread that overwrites it, before it does.
-template <typename T>
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(256)
 sublayer_residual_kernel(float *__restrict__ x, const T *__restrict__ y_dense, const float *__restrict__ y_bias, const T *__restrict__ y_rows,
                          const int *__restrict__ pair_row, const float *__restrict__ pair_weight, int top, const T *__restrict__ y_shared,
@@ -150,11 +151,9 @@ sublayer_residual_kernel(float *__restrict__ x, const T *__restrict__ y_dense, c
     __shared__ float red[33];
     constexpr int V = Elem<T>::kVec;
     const int t = blockIdx.x;
-    // 16-byte pieces when every row starts on a 16-byte boundary (the sums are formed in the same order as element by element)
-    const bool vec = width % V == 0 && ((reinterpret_cast<size_t>(x) | reinterpret_cast<size_t>(y_dense) | reinterpret_cast<size_t>(y_rows) |
-                                         reinterpret_cast<size_t>(y_shared) | reinterpret_cast<size_t>(h_in) | reinterpret_cast<size_t>(h_out) |
-                                         reinterpret_cast<size_t>(trace)) & 15) == 0;
-    const int step = vec ? V : 1;
+    // VEC: 16-byte pieces (every row starts on a 16-byte boundary; the sums are formed in the same order as element by element)
+    constexpr bool vec = VEC;
+    constexpr int step = VEC ? V : 1;
     float inv = 1.0f;
     if (has_y) {
         float ss = 0.0f;
@@ -162,10 +161,10 @@ sublayer_residual_kernel(float *__restrict__ x, const T *__restrict__ y_dense, c
         for (int c = threadIdx.x * step; c < width; c += blockDim.x * step) {
             float v[V];
             if (y_dense) {
-                if (vec) unpack16<T>(ld_v4(y_dense + (size_t)t * width + c), v);
+                if constexpr (vec) unpack16<T>(ld_v4(y_dense + (size_t)t * width + c), v);
                 else v[0] = Elem<T>::to_f(y_dense[(size_t)t * width + c]);
                 if (y_bias)
-                    for (int i = 0; i < step; ++i) v[i] += y_bias[c + i];
+                    _Pragma("unroll") for (int i = 0; i < step; ++i) v[i] += y_bias[c + i];
             } else {
 #pragma unroll
                 for (int i = 0; i < V; ++i) v[i] = 0.0f;
@@ -174,18 +173,18 @@ sublayer_residual_kernel(float *__restrict__ x, const T *__restrict__ y_dense, c
                     const float w = pair_weight ? pair_weight[(size_t)t * top + k] : 1.0f;
                     const T *src = r >= 0 ? y_rows + (size_t)r * width + c : h_in + (size_t)t * width + c;
                     float f[V];
-                    if (vec) unpack16<T>(ld_v4(src), f);
+                    if constexpr (vec) unpack16<T>(ld_v4(src), f);
                     else f[0] = Elem<T>::to_f(src[0]);
-                    for (int i = 0; i < step; ++i) v[i] = fmaf(w, f[i], v[i]);
+                    _Pragma("unroll") for (int i = 0; i < step; ++i) v[i] = fmaf(w, f[i], v[i]);
                 }
                 if (y_shared) {
                     float f[V];
-                    if (vec) unpack16<T>(ld_v4(y_shared + (size_t)t * width + c), f);
+                    if constexpr (vec) unpack16<T>(ld_v4(y_shared + (size_t)t * width + c), f);
                     else f[0] = Elem<T>::to_f(y_shared[(size_t)t * width + c]);
-                    for (int i = 0; i < step; ++i) v[i] = fmaf(sg, f[i], v[i]);
+                    _Pragma("unroll") for (int i = 0; i < step; ++i) v[i] = fmaf(sg, f[i], v[i]);
                 }
             }
-            for (int i = 0; i < step; ++i) {
+            _Pragma("unroll") for (int i = 0; i < step; ++i) {
                 ys[c + i] = v[i];
                 ss = fmaf(v[i], v[i], ss);
             }
@@ -198,7 +197,7 @@ sublayer_residual_kernel(float *__restrict__ x, const T *__restrict__ y_dense, c
     const float a_post = (has_y && norm == B200_NORM_DYT_PRE_POST) ? post[2 * width] : 0.0f, a_pre = pre ? pre[2 * width] : 0.0f;
     for (int c = threadIdx.x * step; c < width; c += blockDim.x * step) {  // a thread reads back the elements of ys it wrote
         float v[V];
-        if (vec) {
+        if constexpr (vec) {
 #pragma unroll
             for (int i = 0; i < V; i += 4) {
                 const float4 xv = *reinterpret_cast<const float4 *>(x + (size_t)t * width + c + i);
@@ -208,13 +207,13 @@ sublayer_residual_kernel(float *__restrict__ x, const T *__restrict__ y_dense, c
             v[0] = x[(size_t)t * width + c];
         }
         if (has_y) {
-            for (int i = 0; i < step; ++i) {
+            _Pragma("unroll") for (int i = 0; i < step; ++i) {
                 float n = norm == B200_NORM_RMS_POST ? ys[c + i] * inv * post[c + i] : dyt_apply(post, width, c + i, a_post, ys[c + i]);
                 if (ls) n *= ls[c + i];
                 v[i] += n;
             }
         }
-        if (vec) {
+        if constexpr (vec) {
 #pragma unroll
             for (int i = 0; i < V; i += 4) {
                 const float4 r = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
@@ -390,6 +389,7 @@ struct b200_hybrid {
     float *x = nullptr, *f32a = nullptr, *f32b = nullptr, *xn = nullptr;
     void *h = nullptr, *proj = nullptr, *mix = nullptr, *mix2 = nullptr, *y = nullptr, *xg = nullptr, *u = nullptr, *yrows = nullptr, *us = nullptr,
          *ys = nullptr, *lqn = nullptr, *lqr = nullptr, *lql = nullptr, *lol = nullptr, *lov = nullptr;
+    float *lpart = nullptr;
     int *meta = nullptr, *moe_i = nullptr;
     float *moe_f = nullptr;
     std::vector<int> host_meta;
@@ -398,7 +398,7 @@ struct b200_hybrid {
 namespace {
 
 struct Carve {
-    size_t x, f32a, f32b, xn, h, proj, mix, y, xg, u, yrows, us, ys, lqn, lqr, lql, lov, meta, moe_i, moe_f, total;
+    size_t x, f32a, f32b, xn, h, proj, mix, y, xg, u, yrows, us, ys, lqn, lqr, lql, lov, lpart, meta, moe_i, moe_f, total;
 };
 
 int max_rows_of(const b200_hybrid_config_t &c, const b200_hybrid_layer_t &l) {
@@ -415,7 +415,7 @@ int n_in_of(const b200_hybrid_layer_t &l) {
 Carve carve(const b200_hybrid *m) {
     const b200_hybrid_config_t &c = m->cfg;
     const size_t T = (size_t)c.max_tokens, es = c.dtype == B200_F32 ? 4 : 2;
-    size_t n_in = 1, n_mix = 1, n_f32 = 1, rows = 0, ff = 1, sff = 1, experts = 1, top = 1, lqn = 0, lqr = 0, lql = 0, lov = 0, lheads = 0;
+    size_t n_in = 1, n_mix = 1, n_f32 = 1, rows = 0, ff = 1, sff = 1, experts = 1, top = 1, lqn = 0, lqr = 0, lql = 0, lov = 0, lheads = 0, lpart = 0;
     const size_t t_pad = (T + 127) / 128 * 128;  // rows per head of the latent mixer's grouped GEMMs
     for (int i = 0; i < c.num_layers; ++i) {
         if (!m->layer_set[i]) continue;
@@ -428,6 +428,7 @@ Carve carve(const b200_hybrid *m) {
             lqn = std::max(lqn, (size_t)l.heads * t_pad * l.dim), lqr = std::max(lqr, T * l.heads * l.rot_dim);
             lql = std::max(lql, (size_t)l.heads * t_pad * l.kv_rank), lov = std::max(lov, (size_t)l.heads * t_pad * l.vdim);
             lheads = std::max(lheads, (size_t)l.heads);
+            lpart = std::max(lpart, (size_t)kLatentPartTiles * l.heads * (l.kv_rank + 2));
         }
         const size_t g = l.gated ? 3 : 1;  // gated: [gate | up] and the product beside it
         if (l.mlp == B200_MLP_MOE) {
@@ -454,6 +455,7 @@ Carve carve(const b200_hybrid *m) {
     k.us = align256(T * sff * es);
     k.ys = align256(T * c.width * es);
     k.lqn = align256(lqn * es), k.lqr = align256(lqr * es), k.lql = align256(lql * es), k.lov = align256(lov * es);
+    k.lpart = align256(lpart * 4);
     // meta: attention tiles [4 * (T/64 + S), padded] | ids | tok_seq | tok_pos | want | short-portion token list [T each] | seq_start [S+1] |
     //       pos0 | slot [S each] | block table [S * mpps]
     //       | latent mixers: one-token tiles of the short portions [4 * T] | head of every row tile of 64 and of 128 [heads * t_pad / 64,
@@ -465,7 +467,7 @@ Carve carve(const b200_hybrid *m) {
     // moe floats: sel_weight [T*top] | row_weight [rows] | shared_gate [T]
     k.moe_f = align256((T * top + rows + T) * 4);
     k.total = k.x + k.f32a + k.f32b + k.xn + k.h + k.proj + 2 * k.mix + k.y + k.xg + k.u + k.yrows + k.us + k.ys + k.lqn + k.lqr + 2 * k.lql +
-              k.lov + k.meta + k.moe_i + k.moe_f;
+              k.lov + k.lpart + k.meta + k.moe_i + k.moe_f;
     return k;
 }
 
@@ -578,6 +580,7 @@ int b200_hybrid_set_scratch(b200_hybrid_t *m, void *ptr, size_t bytes) {
     m->lql = p, p += k.lql;
     m->lol = p, p += k.lql;
     m->lov = p, p += k.lov;
+    m->lpart = (float *)p, p += k.lpart;
     m->meta = (int *)p, p += k.meta;
     m->moe_i = (int *)p, p += k.moe_i;
     m->moe_f = (float *)p, p += k.moe_f;
@@ -753,9 +756,12 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
     auto residual = [&](bool has_y, const void *y_dense, const float *y_bias, const void *y_rows, const int *pair_row, const float *pair_weight, int top,
                         const void *y_shared, const float *gate, int norm, const float *post, const float *ls, const float *pre, float *trace) -> int {
         B200_DISPATCH_DTYPE(dt, {
-            sublayer_residual_kernel<T><<<NT, 256, (size_t)width * sizeof(float), st>>>(
-                m->x, (const T *)y_dense, y_bias, (const T *)y_rows, pair_row, pair_weight, top, (const T *)y_shared, gate, (const T *)m->h, norm, post, ls,
-                c.norm_eps, pre, width, trace, (pre || !f32) ? (T *)m->h : nullptr, has_y ? 1 : 0);
+            // 16-byte pieces when every row starts on a 16-byte boundary (the scratch buffers do; the trace is the caller's)
+            const bool vec = width % Elem<T>::kVec == 0 && (reinterpret_cast<size_t>(trace) & 15) == 0;
+            auto kern = vec ? sublayer_residual_kernel<T, true> : sublayer_residual_kernel<T, false>;
+            kern<<<NT, 256, (size_t)width * sizeof(float), st>>>(m->x, (const T *)y_dense, y_bias, (const T *)y_rows, pair_row, pair_weight, top,
+                                                                (const T *)y_shared, gate, (const T *)m->h, norm, post, ls, c.norm_eps, pre, width, trace,
+                                                                (pre || !f32) ? (T *)m->h : nullptr, has_y ? 1 : 0);
         });
         return cuda_status("sublayer_residual launch");
     };
@@ -813,12 +819,12 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
             const int max_keys = l.window > 0 ? std::min(l.window, mpps * kPageH) : mpps * kPageH;
             if (latent_attention_tiles_supported(dt, l.kv_rank, l.rot_dim)) {
                 RUN(launch_latent_attention_tiles(dt, m->lql, m->lqr, pool, l.sink, m->lol, d_tiles, n_tiles, d_bt, mpps, t_pad, l.heads, l.kv_rank,
-                                                  l.rot_dim, l.scale, l.window, 0, st));
-                // decoded tokens: one tile per token over its heads reads the window once per 64 heads, but is one CTA per token; the per-token
-                // kernel is one CTA per (token, head).  The tile form pays once its CTAs fill half the device.
-                if (l.heads >= kLatentHeadsPerTile && n_short * ((l.heads + 63) / 64) >= 74)
+                                                  l.rot_dim, l.scale, l.window, 0, nullptr, 0, st));
+                // decoded tokens: one tile per token over its heads reads the window once per 64 heads (few tokens share out their keys over
+                // several CTAs); layers of few heads take the per-token kernel, one CTA per (token, head)
+                if (l.heads >= kLatentHeadsPerTile)
                     RUN(launch_latent_attention_tiles(dt, m->lql, m->lqr, pool, l.sink, m->lol, d_stiles, n_short, d_bt, mpps, t_pad, l.heads, l.kv_rank,
-                                                      l.rot_dim, l.scale, l.window, 1, st));
+                                                      l.rot_dim, l.scale, l.window, 1, m->lpart, kLatentPartTiles, st));
                 else
                     RUN(launch_latent_attention(dt, m->lql, m->lqr, pool, l.sink, m->lol, d_seq, d_pos, d_bt, mpps, n_short, t_pad, l.heads, l.kv_rank,
                                                 l.rot_dim, l.scale, l.window, max_keys, st, d_short));

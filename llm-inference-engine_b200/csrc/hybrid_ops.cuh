@@ -25,11 +25,12 @@ int launch_latent_attention(int dtype, const void *ql, const void *qr, const voi
                             const int *tok_pos, const int *block_table, int mpps, int tokens, int t_pad, int heads, int kv_rank, int rot_dim,
                             float scale, int window, int max_keys, cudaStream_t st, const int *tok_list = nullptr);
 // tensor-core form over tiles of <= 64 query rows that share their keys: int4 {sequence, first packed row, rows, first position};
-// by_head == 0: consecutive tokens of one sequence x one head; by_head == 1: one token x 64 consecutive heads
+// by_head == 0: consecutive tokens of one sequence x one head; by_head == 1: one token x 64 consecutive heads.  part (optional, by_head):
+// fp32 [part_tiles, heads, kv_rank + 2] for the partial results when few tiles share out their keys over several CTAs
 bool latent_attention_tiles_supported(int dtype, int kv_rank, int rot_dim);
 int launch_latent_attention_tiles(int dtype, const void *ql, const void *qr, const void *pool, const float *sink, void *ol, const int *tiles,
                                   int n_tiles, const int *block_table, int mpps, int t_pad, int heads, int kv_rank, int rot_dim, float scale,
-                                  int window, int by_head, cudaStream_t st);
+                                  int window, int by_head, float *part, int part_tiles, cudaStream_t st);
 int launch_latent_gate(int dtype, const void *ov, const void *gate_in, int gate_ld, void *out, int tokens, int t_pad, int heads, int vdim,
                        cudaStream_t st);
 
