@@ -430,14 +430,22 @@ latent_combine_kernel(const float *__restrict__ part, const int4 *__restrict__ t
     const int h = blockIdx.y, t = tiles[blockIdx.x].y;
     const size_t stride = (size_t)kv_rank + 2;
     const float *p0 = part + ((size_t)blockIdx.x * splits * heads + h) * stride;
-    float mx = -INFINITY;
-    for (int s = 0; s < splits; ++s) mx = fmaxf(mx, p0[(size_t)s * heads * stride + kv_rank]);
-    float den = 0.0f;
-    for (int s = 0; s < splits; ++s) den += p0[(size_t)s * heads * stride + kv_rank + 1] * exp2f(p0[(size_t)s * heads * stride + kv_rank] - mx);
+    float w[8], mx = -INFINITY, den = 0.0f;  // splits <= 8
+#pragma unroll
+    for (int s = 0; s < 8; ++s) w[s] = s < splits ? p0[(size_t)s * heads * stride + kv_rank] : -INFINITY;
+#pragma unroll
+    for (int s = 0; s < 8; ++s) mx = fmaxf(mx, w[s]);
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+        w[s] = s < splits ? exp2f(w[s] - mx) : 0.0f;
+        if (s < splits) den = fmaf(p0[(size_t)s * heads * stride + kv_rank + 1], w[s], den);
+    }
     const float inv = 1.0f / den;
     for (int c = threadIdx.x; c < kv_rank; c += blockDim.x) {
         float a = 0.0f;
-        for (int s = 0; s < splits; ++s) a = fmaf(p0[(size_t)s * heads * stride + c], exp2f(p0[(size_t)s * heads * stride + kv_rank] - mx), a);
+#pragma unroll
+        for (int s = 0; s < 8; ++s)
+            if (s < splits) a = fmaf(p0[(size_t)s * heads * stride + c], w[s], a);
         ol[((size_t)h * t_pad + t) * kv_rank + c] = Elem<T>::from_f(a * inv);
     }
 }
@@ -446,6 +454,21 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 latent_gate_kernel(const T *__restrict__ ov, const T *__restrict__ gate_in, int gate_ld, T *__restrict__ out, int t_pad, int heads, int vdim) {
     const int t = blockIdx.x;
+    constexpr int V = Elem<T>::kVec;
+    if (vdim % V == 0 && gate_ld % V == 0 &&
+        ((reinterpret_cast<size_t>(ov) | reinterpret_cast<size_t>(gate_in) | reinterpret_cast<size_t>(out)) & 15) == 0) {  // 16-byte pieces
+        const int pieces = vdim / V;
+        for (int idx = threadIdx.x; idx < heads * pieces; idx += blockDim.x) {
+            const int h = idx / pieces, c = (idx - h * pieces) * V;
+            float o[V], z[V];
+            unpack16<T>(ld_v4(ov + ((size_t)h * t_pad + t) * vdim + c), o);
+            unpack16<T>(ld_v4(gate_in + (size_t)t * gate_ld + h * vdim + c), z);
+#pragma unroll
+            for (int e = 0; e < V; ++e) o[e] = o[e] / (1.0f + expf(-z[e]));
+            st_v4(out + ((size_t)t * heads + h) * vdim + c, pack16<T>(o));
+        }
+        return;
+    }
     for (int idx = threadIdx.x; idx < heads * vdim; idx += blockDim.x) {
         const int h = idx / vdim, c = idx - h * vdim;
         const float z = Elem<T>::to_f(gate_in[(size_t)t * gate_ld + idx]);

@@ -129,8 +129,14 @@ postnorm_residual_kernel(float *__restrict__ x, const T *__restrict__ y_dense, c
 }
 
 // packed Dynamic-Tanh parameters: [w (width) | b (width) | alpha]
+// tanh(z) = sign(z) (1 - 2 / (exp(2|z|) + 1)) in fp32 with the hardware exponential and reciprocal: absolute error of a few 1e-7 over the
+// whole range (what fp32 leaves of a value near 1), saturating cleanly; a quarter of the instructions of tanhf, which bounded the kernel
+__device__ __forceinline__ float dyt_tanh(float z) {
+    const float e = __expf(2.0f * fabsf(z));
+    return copysignf(1.0f - __fdividef(2.0f, e + 1.0f), z);
+}
 __device__ __forceinline__ float dyt_apply(const float *__restrict__ p, int width, int c, float alpha, float v) {
-    return fmaf(tanhf(alpha * v), p[c], p[width + c]);
+    return fmaf(dyt_tanh(alpha * v), p[c], p[width + c]);
 }
 
 // The general form of the kernel above, for either norm kind and either place of the routing weights:
