@@ -867,6 +867,8 @@ def run_latent(args):
         return torch.ones(n, dtype=torch.bfloat16)
 
     Tq, B, ctx = args.prefill_tokens, args.batch, args.ctx
+    if ctx % sz["window"] == 0:
+        ctx += sz["window"] // 2  # a context that ends exactly on a chunk edge would leave the chunked model's decoded token a single key to look at
     page = mod.KV_PAGE_SIZE
     per_seq = (max(Tq, ctx + args.steps + args.warmup + 8) + page - 1) // page
     peaks = {}

@@ -138,6 +138,23 @@ __device__ __forceinline__ float dyt_tanh(float z) {
 __device__ __forceinline__ float dyt_apply(const float *__restrict__ p, int width, int c, float alpha, float v) {
     return fmaf(dyt_tanh(alpha * v), p[c], p[width + c]);
 }
+// N (a multiple of 4) consecutive elements from column c on, c and width multiples of 4 and p 16-byte aligned: the parameters arrive in
+// 16-byte loads (a thread's eight scalar loads of consecutive floats are eight separate cache wavefronts per warp)
+template <int N> __device__ __forceinline__ void dyt_apply_vec(const float *__restrict__ p, int width, int c, float alpha, float *v) {
+#pragma unroll
+    for (int i = 0; i < N; i += 4) {
+        const float4 w = *reinterpret_cast<const float4 *>(p + c + i), b = *reinterpret_cast<const float4 *>(p + width + c + i);
+        v[i] = fmaf(dyt_tanh(alpha * v[i]), w.x, b.x), v[i + 1] = fmaf(dyt_tanh(alpha * v[i + 1]), w.y, b.y);
+        v[i + 2] = fmaf(dyt_tanh(alpha * v[i + 2]), w.z, b.z), v[i + 3] = fmaf(dyt_tanh(alpha * v[i + 3]), w.w, b.w);
+    }
+}
+template <int N> __device__ __forceinline__ void load_vec(const float *__restrict__ p, float *v) {
+#pragma unroll
+    for (int i = 0; i < N; i += 4) {
+        const float4 a = *reinterpret_cast<const float4 *>(p + i);
+        v[i] = a.x, v[i + 1] = a.y, v[i + 2] = a.z, v[i + 3] = a.w;
+    }
+}
 
 // The general form of the kernel above, for either norm kind and either place of the routing weights:
 //   y[t, :]  = y_dense[t, :] + y_bias                                                  (a dense sublayer), or
@@ -160,49 +177,55 @@ sublayer_residual_kernel(float *__restrict__ x, const T *__restrict__ y_dense, c
     // VEC: 16-byte pieces (every row starts on a 16-byte boundary; the sums are formed in the same order as element by element)
     constexpr bool vec = VEC;
     constexpr int step = VEC ? V : 1;
+    const float sg = (has_y && !y_dense && y_shared) ? (shared_gate ? shared_gate[t] : 1.0f) : 0.0f;
+    // the sublayer's result for the piece at column c
+    auto result = [&](int c, float *v) {
+        if (y_dense) {
+            if constexpr (vec) unpack16<T>(ld_v4(y_dense + (size_t)t * width + c), v);
+            else v[0] = Elem<T>::to_f(y_dense[(size_t)t * width + c]);
+            if (y_bias) {
+                float b[V];
+                if constexpr (vec) load_vec<V>(y_bias + c, b);
+                else b[0] = y_bias[c];
+                _Pragma("unroll") for (int i = 0; i < step; ++i) v[i] += b[i];
+            }
+            return;
+        }
+        _Pragma("unroll") for (int i = 0; i < step; ++i) v[i] = 0.0f;
+        for (int k = 0; k < top; ++k) {
+            const int r = pair_row[(size_t)t * top + k];
+            const float w = pair_weight ? pair_weight[(size_t)t * top + k] : 1.0f;
+            const T *src = r >= 0 ? y_rows + (size_t)r * width + c : h_in + (size_t)t * width + c;
+            float f[V];
+            if constexpr (vec) unpack16<T>(ld_v4(src), f);
+            else f[0] = Elem<T>::to_f(src[0]);
+            _Pragma("unroll") for (int i = 0; i < step; ++i) v[i] = fmaf(w, f[i], v[i]);
+        }
+        if (y_shared) {
+            float f[V];
+            if constexpr (vec) unpack16<T>(ld_v4(y_shared + (size_t)t * width + c), f);
+            else f[0] = Elem<T>::to_f(y_shared[(size_t)t * width + c]);
+            _Pragma("unroll") for (int i = 0; i < step; ++i) v[i] = fmaf(sg, f[i], v[i]);
+        }
+    };
+    const bool rms = has_y && norm == B200_NORM_RMS_POST;
     float inv = 1.0f;
-    if (has_y) {
+    if (rms) {  // the mean square needs the whole row first: the row waits in shared memory
         float ss = 0.0f;
-        const float sg = (!y_dense && y_shared) ? (shared_gate ? shared_gate[t] : 1.0f) : 0.0f;
         for (int c = threadIdx.x * step; c < width; c += blockDim.x * step) {
             float v[V];
-            if (y_dense) {
-                if constexpr (vec) unpack16<T>(ld_v4(y_dense + (size_t)t * width + c), v);
-                else v[0] = Elem<T>::to_f(y_dense[(size_t)t * width + c]);
-                if (y_bias)
-                    _Pragma("unroll") for (int i = 0; i < step; ++i) v[i] += y_bias[c + i];
-            } else {
-#pragma unroll
-                for (int i = 0; i < V; ++i) v[i] = 0.0f;
-                for (int k = 0; k < top; ++k) {
-                    const int r = pair_row[(size_t)t * top + k];
-                    const float w = pair_weight ? pair_weight[(size_t)t * top + k] : 1.0f;
-                    const T *src = r >= 0 ? y_rows + (size_t)r * width + c : h_in + (size_t)t * width + c;
-                    float f[V];
-                    if constexpr (vec) unpack16<T>(ld_v4(src), f);
-                    else f[0] = Elem<T>::to_f(src[0]);
-                    _Pragma("unroll") for (int i = 0; i < step; ++i) v[i] = fmaf(w, f[i], v[i]);
-                }
-                if (y_shared) {
-                    float f[V];
-                    if constexpr (vec) unpack16<T>(ld_v4(y_shared + (size_t)t * width + c), f);
-                    else f[0] = Elem<T>::to_f(y_shared[(size_t)t * width + c]);
-                    _Pragma("unroll") for (int i = 0; i < step; ++i) v[i] = fmaf(sg, f[i], v[i]);
-                }
-            }
+            result(c, v);
             _Pragma("unroll") for (int i = 0; i < step; ++i) {
                 ys[c + i] = v[i];
                 ss = fmaf(v[i], v[i], ss);
             }
         }
-        if (norm == B200_NORM_RMS_POST) {
-            ss = block_sum(ss, red);
-            inv = rsqrtf(ss / (float)width + eps);
-        }
+        ss = block_sum(ss, red);
+        inv = rsqrtf(ss / (float)width + eps);
     }
-    const float a_post = (has_y && norm == B200_NORM_DYT_PRE_POST) ? post[2 * width] : 0.0f, a_pre = pre ? pre[2 * width] : 0.0f;
-    for (int c = threadIdx.x * step; c < width; c += blockDim.x * step) {  // a thread reads back the elements of ys it wrote
-        float v[V];
+    const float a_post = (has_y && !rms) ? post[2 * width] : 0.0f, a_pre = pre ? pre[2 * width] : 0.0f;
+    for (int c = threadIdx.x * step; c < width; c += blockDim.x * step) {  // (RMS: a thread reads back the elements of ys it wrote)
+        float v[V], y[V];
         if constexpr (vec) {
 #pragma unroll
             for (int i = 0; i < V; i += 4) {
@@ -213,11 +236,22 @@ sublayer_residual_kernel(float *__restrict__ x, const T *__restrict__ y_dense, c
             v[0] = x[(size_t)t * width + c];
         }
         if (has_y) {
-            _Pragma("unroll") for (int i = 0; i < step; ++i) {
-                float n = norm == B200_NORM_RMS_POST ? ys[c + i] * inv * post[c + i] : dyt_apply(post, width, c + i, a_post, ys[c + i]);
-                if (ls) n *= ls[c + i];
-                v[i] += n;
+            float g[V];
+            if (rms) {
+                if constexpr (vec) load_vec<V>(post + c, g);
+                else g[0] = post[c];
+                _Pragma("unroll") for (int i = 0; i < step; ++i) y[i] = ys[c + i] * inv * g[i];
+            } else {  // Dynamic Tanh works element by element: one pass, nothing staged
+                result(c, y);
+                if constexpr (vec) dyt_apply_vec<V>(post, width, c, a_post, y);
+                else y[0] = dyt_apply(post, width, c, a_post, y[0]);
             }
+            if (ls) {
+                if constexpr (vec) load_vec<V>(ls + c, g);
+                else g[0] = ls[c];
+                _Pragma("unroll") for (int i = 0; i < step; ++i) y[i] *= g[i];
+            }
+            _Pragma("unroll") for (int i = 0; i < step; ++i) v[i] += y[i];
         }
         if constexpr (vec) {
 #pragma unroll
@@ -227,9 +261,7 @@ sublayer_residual_kernel(float *__restrict__ x, const T *__restrict__ y_dense, c
                 if (trace) *reinterpret_cast<float4 *>(trace + (size_t)t * width + c + i) = r;
             }
             if (h_out) {
-                if (pre)
-#pragma unroll
-                    for (int i = 0; i < V; ++i) v[i] = dyt_apply(pre, width, c + i, a_pre, v[i]);
+                if (pre) dyt_apply_vec<V>(pre, width, c, a_pre, v);
                 st_v4(h_out + (size_t)t * width + c, pack16<T>(v));
             }
         } else {
@@ -763,7 +795,8 @@ int b200_hybrid_forward(b200_hybrid_t *m, const b200_hybrid_batch_t *b, float *l
                         const void *y_shared, const float *gate, int norm, const float *post, const float *ls, const float *pre, float *trace) -> int {
         B200_DISPATCH_DTYPE(dt, {
             // 16-byte pieces when every row starts on a 16-byte boundary (the scratch buffers do; the trace is the caller's)
-            const bool vec = width % Elem<T>::kVec == 0 && (reinterpret_cast<size_t>(trace) & 15) == 0;
+            const bool vec = width % Elem<T>::kVec == 0 && ((reinterpret_cast<size_t>(trace) | reinterpret_cast<size_t>(post) | reinterpret_cast<size_t>(ls) |
+                                                              reinterpret_cast<size_t>(pre) | reinterpret_cast<size_t>(y_bias)) & 15) == 0;
             auto kern = vec ? sublayer_residual_kernel<T, true> : sublayer_residual_kernel<T, false>;
             kern<<<NT, 256, (size_t)width * sizeof(float), st>>>(m->x, (const T *)y_dense, y_bias, (const T *)y_rows, pair_row, pair_weight, top,
                                                                 (const T *)y_shared, gate, (const T *)m->h, norm, post, ls, c.norm_eps, pre, width, trace,

@@ -205,16 +205,21 @@ __global__ void gated_activation_kernel(const T *__restrict__ in, T *__restrict_
 template <typename T>
 __global__ void bias_activation_kernel(T *__restrict__ x, const float *__restrict__ bias, size_t rows, int cols, int act) {
     constexpr int V = Elem<T>::kVec;
-    if (cols % V == 0 && (reinterpret_cast<size_t>(x) & 15) == 0) {
+    if (cols % V == 0 && ((reinterpret_cast<size_t>(x) | reinterpret_cast<size_t>(bias)) & 15) == 0) {
         const int per_row = cols / V;
         const size_t n = rows * per_row;
         for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
             const int c = (int)(i % per_row) * V;
-            float f[V];
+            float f[V], b[V];
             unpack16<T>(ld_v4(x + i * V), f);
 #pragma unroll
+            for (int e = 0; e < V; e += 4) {  // the bias in 16-byte loads: eight scalar loads per thread are eight cache wavefronts per warp
+                const float4 bv = bias ? *reinterpret_cast<const float4 *>(bias + c + e) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                b[e] = bv.x, b[e + 1] = bv.y, b[e + 2] = bv.z, b[e + 3] = bv.w;
+            }
+#pragma unroll
             for (int e = 0; e < V; ++e) {
-                const float v = f[e] + (bias ? bias[c + e] : 0.0f);
+                const float v = f[e] + b[e];
                 f[e] = act >= 0 ? act_apply(v, act) : v;
             }
             st_v4(x + i * V, pack16<T>(f));
