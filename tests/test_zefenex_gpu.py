@@ -322,8 +322,8 @@ def test_tensor_core_attention_edges_with_a_dominant_key(window, query_pos, key_
 def test_tensor_core_paths_against_the_oracle_and_against_single_tokens(dtype):
     """Sizes every tensor-core path takes: tiles of prompt tokens, one-token tiles over 20 heads, a rank of 256 in two value blocks, and --
     with a prompt of 300 tokens -- the head products on 128-row tiles.  Portions that start in the middle of a page and of a window."""
-    layers = [ref.latent_layer(heads=4, dim=64, rot_dim=32, vdim=80, kv_rank=96, window=40, mlp=ref.dense()),
-              ref.latent_layer(heads=20, dim=64, rot_dim=32, vdim=64, kv_rank=96, window=150, kv_from=0, mlp=ref.moe(experts=2, identity=1, top=3)),
+    layers = [ref.latent_layer(heads=6, dim=64, rot_dim=16, vdim=48, kv_rank=80, window=36, mlp=ref.dense()),
+              ref.latent_layer(heads=20, dim=64, rot_dim=16, vdim=64, kv_rank=80, window=150, kv_from=0, mlp=ref.moe(experts=2, identity=1, top=3)),
               ref.latent_layer(heads=2, dim=64, rot_dim=16, vdim=24, kv_rank=256, window=70, scale=0.1)]
     config = ref.make_config(layers, width=64)
     W, packed = ref.make_weights(config, seed=41)
