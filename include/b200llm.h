@@ -564,6 +564,35 @@ int b200_gla_recurrent(const void *proj, int ld, const float *decay, float *stat
 int b200_moe_route_sigmoid(const float *logits, int ld, int *sel_expert, float *sel_weight, float *shared_gate, int tokens, int experts,
                            int top, b200_stream_t stream);
 
+/* Router of a softmax-scored mixture of experts.  logits fp32 [tokens, ld], `outputs` router outputs (real experts first, identity
+ * experts after them).  Scores = softmax over the outputs; the `top` largest of score + bias (bias NULL: none; ties: lower index) are
+ * chosen; sel_weight = the chosen scores / (their sum + 1e-20). */
+int b200_moe_route_softmax(const float *logits, int ld, const float *bias, int *sel_expert, float *sel_weight, int tokens, int outputs,
+                           int top, b200_stream_t stream);
+/* Latent attention (B200_MIXER_LATENT) over a paged pool of rows [c (kv_rank) | kr (rot_dim)], [num_pages, B200_KV_PAGE_SIZE, kv_rank +
+ * rot_dim] of `dtype`.  Rows of the per-head tensors are grouped head by head: [heads, t_pad, *] with t_pad >= tokens.
+ * prep: proj [tokens, ld] holds the queries at column q_col (per head [dim | rot_dim]) and, if kv_col >= 0, the down-projection (kv_rank
+ *   + rot_dim) at column kv_col.  qn [heads, t_pad, dim] <- the un-rotated query parts; qr [tokens, heads, rot_dim] <- the rotated parts
+ *   (pairs i, i + rot_dims/2 of the first rot_dims dimensions, angle pos * rot_base^(-2i/rot_dims)); with kv_col >= 0 the pool row of
+ *   (sequence, position) <- [rmsnorm(first kv_rank) * kv_norm | rotated rest].
+ * attention: ql [heads, t_pad, kv_rank] (the queries moved into the latent space), qr as above -> ol [heads, t_pad, kv_rank] =
+ *   sum_j p(i, j) c_j with p the softmax of scale * (ql . c_j + qr . kr_j) over the window 0 <= i - j < window (0: plain causal) and one
+ *   sink logit per head (NULL: none) in the denominator.  One CTA per (token, head).
+ * attention_tiles: the same on the tensor cores (16-bit dtypes; B200_ERR_UNSUPPORTED for sizes it does not take) over tiles int4
+ *   {sequence, first packed row, rows <= 64, first position}: by_head == 0: consecutive tokens of one sequence x one head; by_head == 1:
+ *   one token x all heads.  part (optional, by_head): fp32 [part_tiles, heads, kv_rank + 2] scratch that lets few tiles share out their
+ *   keys over several CTAs. */
+int b200_latent_prep_paged(const void *proj, int ld, int q_col, int kv_col, void *qn, void *qr, void *pool, const float *kv_norm, float eps,
+                           const int *tok_seq, const int *tok_pos, const int *block_table, int max_pages_per_seq, int tokens, int t_pad,
+                           int heads, int dim, int rot_dim, int kv_rank, int rot_dims, float rot_base, int dtype, b200_stream_t stream);
+int b200_latent_attention_paged(const void *ql, const void *qr, const void *pool, const float *sink, void *ol, const int *tok_seq,
+                                const int *tok_pos, const int *block_table, int max_pages_per_seq, int tokens, int t_pad, int heads,
+                                int kv_rank, int rot_dim, float scale, int window, int dtype, b200_stream_t stream);
+int b200_latent_attention_tiles_paged(const void *ql, const void *qr, const void *pool, const float *sink, void *ol, const int *tiles,
+                                      int n_tiles, const int *block_table, int max_pages_per_seq, int t_pad, int heads, int kv_rank,
+                                      int rot_dim, float scale, int window, int by_head, float *part, int part_tiles, int dtype,
+                                      b200_stream_t stream);
+
 /* ========================================== generation loop ========================================= */
 
 /* The loop LlamaModel<T>::response / generateFirstToken / generateNextToken / LMHeadAndTopKSample intend

@@ -192,6 +192,10 @@ SIGNATURES = {
     "b200_chunked_attention_prefill_paged": [_P, _P, _P, _P, _P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _F, _I, _I, _P],
     "b200_gla_recurrent": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "b200_moe_route_sigmoid": [_P, _I, _P, _P, _P, _I, _I, _I, _P],
+    "b200_moe_route_softmax": [_P, _I, _P, _P, _P, _I, _I, _I, _P],
+    "b200_latent_prep_paged": [_P, _I, _I, _I, _P, _P, _P, _P, _F, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+    "b200_latent_attention_paged": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P],
+    "b200_latent_attention_tiles_paged": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P, _I, _I, _P],
     "b200_batcher_set_state_slots": [_P, _I],
     "b200_batcher_free_slots": [_P],
     "b200_batcher_set_chunk": [_P, _I],
@@ -563,6 +567,52 @@ def moe_route_sigmoid(logits, experts, top, with_shared_gate=True):
     gate = torch.empty(n, dtype=torch.float32, device=logits.device) if with_shared_gate else None
     check(lib().b200_moe_route_sigmoid(ptr(logits), logits.shape[1], ptr(sel), ptr(w), ptr(gate), n, experts, top, stream()))
     return sel, w, gate
+
+
+def moe_route_softmax(logits, bias, top):
+    """logits fp32 [tokens, outputs], bias fp32 [outputs] or None -> (chosen int32 [tokens, top], weights fp32 [tokens, top])."""
+    torch = _torch()
+    n = logits.shape[0]
+    sel = torch.empty((n, top), dtype=torch.int32, device=logits.device)
+    w = torch.empty((n, top), dtype=torch.float32, device=logits.device)
+    check(lib().b200_moe_route_softmax(ptr(logits), logits.shape[1], ptr(bias), ptr(sel), ptr(w), n, logits.shape[1], top, stream()))
+    return sel, w
+
+
+def latent_prep_paged(proj, heads, dim, rot_dim, kv_rank, rot_dims, rot_base, kv_norm, eps, tok_seq, tok_pos, block_table, pool, t_pad, append=True):
+    """proj [tokens, heads*(dim+rot_dim) (+ kv_rank+rot_dim)]: queries first, then -- with append -- the down-projection.
+    -> (qn [heads, t_pad, dim], qr [tokens, heads, rot_dim]); with append the rows [normed c | rotated kr] go to the pool."""
+    torch = _torch()
+    n = proj.shape[0]
+    qn = torch.zeros((heads, t_pad, dim), dtype=proj.dtype, device=proj.device)
+    qr = torch.zeros((n, heads, max(rot_dim, 1)), dtype=proj.dtype, device=proj.device)
+    check(lib().b200_latent_prep_paged(ptr(proj), proj.shape[1], 0, heads * (dim + rot_dim) if append else -1, ptr(qn), ptr(qr), ptr(pool),
+                                       ptr(kv_norm), eps, ptr(tok_seq), ptr(tok_pos), ptr(block_table), block_table.shape[1], n, t_pad, heads, dim,
+                                       rot_dim, kv_rank, rot_dims, rot_base, dtype_code(proj), stream()))
+    return qn, qr
+
+
+def latent_attention_paged(ql, qr, pool, sink, tok_seq, tok_pos, block_table, rot_dim, scale, window):
+    """ql [heads, t_pad, kv_rank], qr [tokens, heads, rot_dim] -> ol [heads, t_pad, kv_rank] (rows of the batch's tokens)."""
+    torch = _torch()
+    heads, t_pad, kv_rank = ql.shape
+    ol = torch.zeros_like(ql)
+    check(lib().b200_latent_attention_paged(ptr(ql), ptr(qr), ptr(pool), ptr(sink), ptr(ol), ptr(tok_seq), ptr(tok_pos), ptr(block_table),
+                                            block_table.shape[1], tok_seq.shape[0], t_pad, heads, kv_rank, rot_dim, scale, window, dtype_code(ql),
+                                            stream()))
+    return ol
+
+
+def latent_attention_tiles_paged(ql, qr, pool, sink, tiles, block_table, rot_dim, scale, window, by_head=False, part_tiles=0):
+    """The tensor-core variant.  tiles: int32 [n, 4] device tensor {sequence, first row, rows <= 64, first position}."""
+    torch = _torch()
+    heads, t_pad, kv_rank = ql.shape
+    ol = torch.zeros_like(ql)
+    part = torch.empty((part_tiles, heads, kv_rank + 2), dtype=torch.float32, device=ql.device) if part_tiles else None
+    check(lib().b200_latent_attention_tiles_paged(ptr(ql), ptr(qr), ptr(pool), ptr(sink), ptr(ol), ptr(tiles), tiles.shape[0], ptr(block_table),
+                                                  block_table.shape[1], t_pad, heads, kv_rank, rot_dim, scale, window, 1 if by_head else 0, ptr(part),
+                                                  part_tiles, dtype_code(ql), stream()))
+    return ol
 
 
 class Decoder:

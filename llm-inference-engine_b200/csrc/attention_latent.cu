@@ -586,3 +586,44 @@ int launch_latent_gate(int dtype, const void *ov, const void *gate_in, int gate_
 }
 
 }  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_latent_prep_paged(const void *proj, int ld, int q_col, int kv_col, void *qn, void *qr, void *pool, const float *kv_norm, float eps,
+                           const int *tok_seq, const int *tok_pos, const int *block_table, int max_pages_per_seq, int tokens, int t_pad,
+                           int heads, int dim, int rot_dim, int kv_rank, int rot_dims, float rot_base, int dtype, b200_stream_t stream) {
+    B200_REQUIRE(proj && qn && (qr || rot_dim == 0) && tok_seq && tok_pos && block_table, "latent_prep: null pointer");
+    B200_REQUIRE(kv_col < 0 || (pool && kv_norm), "latent_prep: a layer that appends rows needs the pool and the row norm weight");
+    B200_REQUIRE(tokens >= 0 && t_pad >= tokens && heads > 0 && dim > 0 && rot_dim >= 0 && kv_rank > 0 && q_col >= 0 &&
+                     ld >= q_col + heads * (dim + rot_dim) && (kv_col < 0 || ld >= kv_col + kv_rank + rot_dim),
+                 "latent_prep: bad shape");
+    B200_REQUIRE(rot_dims >= 0 && rot_dims <= rot_dim && rot_dims % 2 == 0 && (rot_dims == 0 || rot_base > 0.0f), "latent_prep: bad rotation");
+    return launch_latent_prep(dtype, proj, ld, q_col, kv_col, qn, qr, pool, kv_norm, eps, tok_seq, tok_pos, block_table, max_pages_per_seq, tokens,
+                              t_pad, heads, dim, rot_dim, kv_rank, rot_dims, rot_base, as_stream(stream));
+}
+
+int b200_latent_attention_paged(const void *ql, const void *qr, const void *pool, const float *sink, void *ol, const int *tok_seq,
+                                const int *tok_pos, const int *block_table, int max_pages_per_seq, int tokens, int t_pad, int heads,
+                                int kv_rank, int rot_dim, float scale, int window, int dtype, b200_stream_t stream) {
+    B200_REQUIRE(ql && (qr || rot_dim == 0) && pool && ol && tok_seq && tok_pos && block_table, "latent_attention: null pointer");
+    B200_REQUIRE(tokens >= 0 && t_pad >= tokens && heads > 0 && kv_rank > 0 && rot_dim >= 0 && window >= 0 && max_pages_per_seq > 0,
+                 "latent_attention: bad shape");
+    const int all = max_pages_per_seq * B200_KV_PAGE_SIZE;
+    return launch_latent_attention(dtype, ql, qr, pool, sink, ol, tok_seq, tok_pos, block_table, max_pages_per_seq, tokens, t_pad, heads, kv_rank,
+                                   rot_dim, scale, window, window > 0 ? std::min(window, all) : all, as_stream(stream), nullptr);
+}
+
+int b200_latent_attention_tiles_paged(const void *ql, const void *qr, const void *pool, const float *sink, void *ol, const int *tiles,
+                                      int n_tiles, const int *block_table, int max_pages_per_seq, int t_pad, int heads, int kv_rank,
+                                      int rot_dim, float scale, int window, int by_head, float *part, int part_tiles, int dtype,
+                                      b200_stream_t stream) {
+    B200_REQUIRE(ql && (qr || rot_dim == 0) && pool && ol && tiles && block_table, "latent_attention_tiles: null pointer");
+    B200_REQUIRE(n_tiles >= 0 && heads > 0 && kv_rank > 0 && rot_dim >= 0 && window >= 0 && t_pad > 0, "latent_attention_tiles: bad shape");
+    B200_REQUIRE(((uintptr_t)tiles & 15) == 0, "latent_attention_tiles: the tile list must be 16-byte aligned");
+    B200_REQUIRE(!part || part_tiles >= n_tiles, "latent_attention_tiles: the partial-result scratch holds %d tiles, %d given", part_tiles, n_tiles);
+    return launch_latent_attention_tiles(dtype, ql, qr, pool, sink, ol, tiles, n_tiles, block_table, max_pages_per_seq, t_pad, heads, kv_rank, rot_dim,
+                                         scale, window, by_head, part, part_tiles, as_stream(stream));
+}
+}

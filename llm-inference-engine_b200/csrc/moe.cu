@@ -504,3 +504,10 @@ extern "C" int b200_moe_route_sigmoid(const float *logits, int ld, int *sel_expe
     B200_REQUIRE(tokens >= 0 && experts > 0 && top > 0 && top <= experts && ld >= experts + (shared_gate ? 1 : 0), "moe_route: bad shape");
     return launch_moe_route_sigmoid(logits, ld, sel_expert, sel_weight, shared_gate, tokens, experts, top, as_stream(stream));
 }
+
+extern "C" int b200_moe_route_softmax(const float *logits, int ld, const float *bias, int *sel_expert, float *sel_weight, int tokens, int outputs,
+                                      int top, b200_stream_t stream) {
+    B200_REQUIRE(logits && sel_expert && sel_weight, "moe_route_softmax: null pointer");
+    B200_REQUIRE(tokens >= 0 && outputs > 0 && top > 0 && top <= outputs && ld >= outputs, "moe_route_softmax: bad shape");
+    return launch_moe_route_softmax(logits, ld, bias, sel_expert, sel_weight, tokens, outputs, top, as_stream(stream));
+}

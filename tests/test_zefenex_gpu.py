@@ -389,6 +389,93 @@ def test_pool_exhaustion_is_refused_not_overwritten():
     assert ref.rel_err(got, want_logits(config, W, tokens_of(config, 10, 2))[[9]]) < 5e-5
 
 
+# ------------------------------------------------------------------ the mechanisms' own launchers
+def test_softmax_router_picks_and_weights():
+    m = b200()
+    g = torch.Generator().manual_seed(0)
+    z = (2.0 * torch.randn(37, 11, generator=g)).to(DEV)
+    bias = (0.1 * torch.randn(11, generator=g)).to(DEV)
+    for b in (bias, None):
+        sel, w = m.moe_route_softmax(z, b, 3)
+        s = torch.softmax(z.double(), -1)
+        _, ti = torch.topk(s + (b.double() if b is not None else 0.0), 3, dim=-1)
+        tv = torch.gather(s, 1, ti)
+        assert torch.equal(sel.long().cpu(), ti.cpu())
+        assert torch.allclose(w.double().cpu(), (tv / tv.sum(-1, keepdim=True)).cpu(), rtol=1e-5)
+
+
+def test_latent_prep_against_the_plain_computation():
+    m = b200()
+    H, d, dr, dims, r, base, eps = 3, 12, 10, 6, 20, 300.0, 1e-5
+    g = torch.Generator().manual_seed(2)
+    T = 70
+    proj = torch.randn(T, H * (d + dr) + r + dr, generator=g).to(DEV)
+    w = (1.0 + 0.3 * torch.randn(r, generator=g)).to(DEV)
+    pool = torch.full((4, 64, r + dr), float("nan"), device=DEV)
+    bt = torch.tensor([[2, 0, -1], [3, -1, -1]], dtype=torch.int32, device=DEV)
+    seq = torch.tensor([0] * 60 + [1] * 10, dtype=torch.int32, device=DEV)
+    pos = torch.tensor(list(range(30, 90)) + list(range(10)), dtype=torch.int32, device=DEV)   # sequence 0 crosses from page 2 to page 0
+    qn, qr = m.latent_prep_paged(proj, H, d, dr, r, dims, base, w, eps, seq, pos, bt, pool, 128)
+    torch.cuda.synchronize()
+    p64, q = proj.cpu().double(), proj.cpu().double()[:, :H * (d + dr)].view(T, H, d + dr)
+    assert torch.equal(qn[:, :T].cpu().double(), q[..., :d].transpose(0, 1))
+    assert torch.allclose(qr.cpu().double(), ref.rotate(q[..., d:], pos.cpu(), base, dims), rtol=1e-5, atol=1e-6)
+    down = p64[:, H * (d + dr):]
+    rows = torch.cat([ref.rms_unit(down[:, :r], eps) * w.cpu().double(), ref.rotate(down[:, r:], pos.cpu(), base, dims)], -1)
+    for t in range(T):
+        page = int(bt[int(seq[t]), int(pos[t]) // 64])
+        assert torch.allclose(pool[page, int(pos[t]) % 64].cpu().double(), rows[t], rtol=1e-5, atol=1e-6), t
+    assert torch.isnan(pool[1]).all() and torch.isnan(pool[3, 10:]).all()   # nothing else was written
+
+
+def _latent_tiles(portions):
+    out = []
+    for s, row0, n, pos0 in portions:
+        for a in range(0, n, 64):
+            out.append([s, row0 + a, min(64, n - a), pos0 + a])
+    return torch.tensor(out, dtype=torch.int32, device=DEV)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "f16"])
+@pytest.mark.parametrize("heads,rank,rot,window", [(4, 32, 16, 48), (3, 96, 32, 100), (20, 48, 16, 1000), (2, 256, 0, 70), (70, 16, 16, 130),
+                                                   (2, 384, 64, 0), (5, 192, 64, 64)])
+def test_latent_tensor_core_kernels_match_the_per_token_kernel(heads, rank, rot, window, dtype):
+    m = b200()
+    pages, t_pad = 12, 448
+    g = torch.Generator().manual_seed(heads + rank + window)
+    # sequence 0: 37 cached positions, then a portion of 203; sequence 1: a portion of 130 from position 0; then one more token of each
+    bt = torch.tensor([[7, 1, 10, 4, -1, -1], [3, 9, 0, -1, -1, -1]], dtype=torch.int32, device=DEV)
+    pool = torch.full((pages, 64, rank + rot), float("nan"), dtype=dtype, device=DEV)
+    rows = {0: torch.randn(241, rank + rot, generator=g).to(dtype).to(DEV), 1: torch.randn(131, rank + rot, generator=g).to(dtype).to(DEV)}
+    for s_, n in ((0, 240), (1, 130)):
+        for p_ in range(n):
+            pool[int(bt[s_, p_ // 64]), p_ % 64] = rows[s_][p_]
+    seq = torch.tensor([0] * 203 + [1] * 130, dtype=torch.int32, device=DEV)
+    pos = torch.tensor(list(range(37, 240)) + list(range(130)), dtype=torch.int32, device=DEV)
+    T = 333
+    ql = (0.3 * torch.randn(heads, t_pad, rank, generator=g)).to(dtype).to(DEV)
+    qr = (0.3 * torch.randn(T, heads, max(rot, 1), generator=g)).to(dtype).to(DEV)
+    sink = torch.linspace(-2.0, 3.0, heads).to(DEV)
+    want = m.latent_attention_paged(ql, qr, pool, sink, seq, pos, bt, rot, 0.2, window)
+    got = m.latent_attention_tiles_paged(ql, qr, pool, sink, _latent_tiles([(0, 0, 203, 37), (1, 203, 130, 0)]), bt, rot, 0.2, window)
+    torch.cuda.synchronize()
+    assert not torch.isnan(got[:, :T]).any() and not torch.isnan(want[:, :T]).any()
+    scale_ = want[:, :T].float().abs().max().item()
+    assert (got[:, :T].float() - want[:, :T].float()).abs().max().item() < 1.5e-2 * scale_
+    # decoded tokens: the next position of each sequence, as one-token tiles over the heads, alone and with their keys shared out
+    pool[int(bt[0, 240 // 64]), 240 % 64] = rows[0][240]
+    pool[int(bt[1, 130 // 64]), 130 % 64] = rows[1][130]
+    seq2 = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
+    pos2 = torch.tensor([240, 130], dtype=torch.int32, device=DEV)
+    want2 = m.latent_attention_paged(ql, qr, pool, sink, seq2, pos2, bt, rot, 0.2, window)
+    tiles2 = torch.tensor([[0, 0, 1, 240], [1, 1, 1, 130]], dtype=torch.int32, device=DEV)
+    for part_tiles in (0, 2, 16):   # no shares; scratch for one share each; eight shares each
+        got2 = m.latent_attention_tiles_paged(ql, qr, pool, sink, tiles2, bt, rot, 0.2, window, by_head=True, part_tiles=part_tiles)
+        torch.cuda.synchronize()
+        assert not torch.isnan(got2[:, :2]).any()
+        assert (got2[:, :2].float() - want2[:, :2].float()).abs().max().item() < 1.5e-2 * want2[:, :2].float().abs().max().item(), part_tiles
+
+
 # ------------------------------------------------------------------ the scheduler's own entry point, the registry, the command line
 @pytest.mark.parametrize("chunk", [0, 5])
 def test_greedy_generation_through_the_scheduler(chunk):
